@@ -1,0 +1,113 @@
+/*
+ * int4linear_b200 -- C ABI of the Blackwell (sm_100a) INT4 linear layer
+ *
+ *     Y[M x N] (int32) = X[M x K] (s4) * W[N x K]^T (s4)
+ *
+ * Operand format (identical to myeongs-song/Int4Linear):
+ *   X  M rows of K signed 4-bit values, two per byte, low nibble = even index,
+ *      i.e. eight per little-endian 32-bit word exactly as utils/packer.cpp:3-18
+ *      writes them; row pitch K/2 bytes.
+ *   W  N rows of K values in the same packing ("column-major K x N").
+ *   Y  M x N int32, row-major, fully overwritten.
+ *
+ * Shape contract: m, n, k > 0; k % 32 == 0 (16-byte row pitch); k < 131072
+ * (the kernels multiply 16*x by 16*w in int32 and shift the sum back).
+ * X, W and Y must be 16-byte aligned.  Any m and n are accepted.
+ *
+ * All functions are thread-safe per device.  Nothing here falls back to a
+ * CPU implementation: without an sm_100 GPU every compute entry point fails
+ * with INT4L_ERR_NO_DEVICE.
+ */
+#ifndef INT4LINEAR_B200_H_
+#define INT4LINEAR_B200_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes returned by the int-returning entry points and by
+ * int4_linear_last_status(). */
+#define INT4L_OK                  0
+#define INT4L_ERR_INVALID_ARG     1  /* null pointer or non-positive dimension   */
+#define INT4L_ERR_UNSUPPORTED     2  /* k % 32 != 0 or k >= 131072               */
+#define INT4L_ERR_MISALIGNED      3  /* a pointer is not 16-byte aligned         */
+#define INT4L_ERR_CUDA            4  /* a CUDA runtime/driver call failed        */
+#define INT4L_ERR_DEVICE_TIMEOUT  5  /* a bounded in-kernel wait expired         */
+#define INT4L_ERR_NO_DEVICE       6  /* current device is not sm_100             */
+#define INT4L_ERR_TOO_LARGE       7  /* size beyond a fixed-capacity entry point */
+
+/* Kernel families selectable with int4_linear_set_path(). */
+#define INT4L_PATH_AUTO     0  /* shape dispatch (default)                                   */
+#define INT4L_PATH_TCGEN05  1  /* TMA -> s4->s8 unpack -> tcgen05.mma kind::i8 -> TMEM        */
+#define INT4L_PATH_LEGACY   2  /* warp-level mma.sync m16n8k64 s4 (pre-Blackwell instruction) */
+#define INT4L_PATH_SKINNY   3  /* register-streaming kernel for m <= 64 (decode shapes)      */
+
+/*
+ * Drop-in for `void linear_v21_launch(void*, void*, void*, int, int, int)`
+ * (kernels/linear_v21.h:760, body kernels/linear_v21.cu:9-49): device
+ * pointers, current device, default stream, returns after the result is
+ * complete (the reference ends with cudaDeviceSynchronize, linear_v21.cu:39).
+ * Like the reference it returns nothing; on failure it prints one
+ * "CUDA FAILED: ..." line to stderr (the reference's wording,
+ * kernels/linear_v10.cu:33-38) and records the code for
+ * int4_linear_last_status().  The library also exports the C++ symbol
+ * linear_v21_launch with the same behaviour so the reference's
+ * test/test_correctness.cu links unchanged.
+ */
+void int4_linear_launch(void* x_packed_d, void* w_packed_d, void* y_d, int m, int n, int k);
+
+/*
+ * Same operator, asynchronous on `stream` (a cudaStream_t; NULL = default
+ * stream) and returning a status code.  No reference counterpart: the
+ * reference launcher is blocking; this is what a multi-GPU driver or a graph
+ * capture needs.  A device-side timeout is only visible later through
+ * int4_linear_last_status().
+ */
+int int4_linear_launch_async(const void* x_packed_d, const void* w_packed_d, void* y_d,
+                             int m, int n, int k, void* stream);
+
+/*
+ * Host-buffer form of the call sequence in test/test_correctness.cu:53-63
+ * (cudaMalloc x3, cudaMemcpy H2D x2, launch, cudaMemcpy D2H): operands and
+ * result live in host memory; the library stages them through device buffers
+ * it keeps between calls.  `w_resident` != 0 says the weights behind
+ * `w_packed_h` are unchanged since the previous call with the same pointer
+ * and size, so their upload is skipped (a linear layer's weights are
+ * stationary; activations and the result always move).
+ */
+int int4_linear_host(const void* x_packed_h, const void* w_packed_h, void* y_h,
+                     int m, int n, int k, int w_resident);
+
+/* Status of the most recent call on the current device; also polls the word
+ * the kernels raise when a bounded wait expires (and clears it). */
+int int4_linear_last_status(void);
+
+/* Static string for a status code. */
+const char* int4_linear_status_string(int status);
+
+/* Forces one kernel family (INT4L_PATH_*) for subsequent calls of this
+ * process; returns the previous setting.  The environment variable
+ * INT4L_PATH=auto|tcgen05|legacy|skinny sets the initial value. */
+int int4_linear_set_path(int path);
+
+/* Tuning overrides for the tcgen05 family, for experiments and tests:
+ * tile_n in {0 = automatic, 64, 128, 256} fixes the N extent of the output
+ * tile; direct_store != 0 makes the epilogue write Y with per-thread vector
+ * stores instead of shared-memory staging + TMA stores (always used when
+ * n % 4 != 0).  Environment: INT4L_TILE_N, INT4L_EPILOGUE=direct. */
+int int4_linear_set_tuning(int tile_n, int direct_store);
+
+/* Which family the dispatcher would use for a shape (INT4L_PATH_*). */
+int int4_linear_path_for(int m, int n, int k);
+
+/* Number of kernels this library has launched in this process. */
+long long int4_linear_launch_count(void);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int int4_linear_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* INT4LINEAR_B200_H_ */

@@ -1,0 +1,54 @@
+"""Compile the CUDA sources of this package into libint4linear_b200.so (in-tree).
+
+    python -m int4linear_b200.build [--force] [--verbose]
+
+nvcc cross-compiles for sm_100a without a GPU, so this runs anywhere the CUDA
+toolkit is installed.  The shared library links the CUDA runtime statically
+and resolves the one driver entry point it needs at run time, so it loads on a
+machine without a driver too (its compute entry points then report
+INT4L_ERR_NO_DEVICE).
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG, "csrc")
+LIB = os.path.join(PKG, "libint4linear_b200.so")
+SOURCES = ["api.cu", "gemm_tcgen05.cu", "gemm_skinny.cu", "gemm_legacy.cu"]
+
+
+def _deps() -> list[str]:
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    deps.append(os.path.join(os.path.dirname(PKG), "include", "int4linear_b200.h"))
+    return deps
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    return any(os.path.getmtime(d) > t for d in _deps())
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not needs_build():
+        return LIB
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found; cannot build libint4linear_b200.so")
+    cmd = [nvcc, "-std=c++17", "-O3", "-shared", "-Xcompiler", "-fPIC",
+           "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+           "-cudart", "static", "-o", LIB]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES]
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,321 @@
+// C-ABI layer: argument checking, per-device set-up, shape dispatch, the
+// blocking / asynchronous / host-buffer entry points, and status reporting.
+// Mirrors the host launcher of the reference, kernels/linear_v21.cu:9-49.
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "common.h"
+
+namespace i4l {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+DeviceCtx g_ctx[kMaxDevices];
+bool g_ctx_ready[kMaxDevices];
+std::mutex g_mutex;
+std::atomic<long long> g_launches{0};
+std::atomic<int> g_path{-1};       // -1 = not yet read from the environment
+std::atomic<int> g_tile_n{0};      // 0 = automatic
+std::atomic<int> g_direct_store{-1};
+thread_local int t_last_status = INT4L_OK;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int path_from_env()
+{
+    const char* e = std::getenv("INT4L_PATH");
+    if (!e) return INT4L_PATH_AUTO;
+    if (!std::strcmp(e, "tcgen05")) return INT4L_PATH_TCGEN05;
+    if (!std::strcmp(e, "legacy")) return INT4L_PATH_LEGACY;
+    if (!std::strcmp(e, "skinny")) return INT4L_PATH_SKINNY;
+    return INT4L_PATH_AUTO;
+}
+
+int current_path()
+{
+    int p = g_path.load();
+    if (p < 0) { p = path_from_env(); g_path.store(p); }
+    return p;
+}
+
+int check_args(const void* x, const void* w, const void* y, int m, int n, int k)
+{
+    if (!x || !w || !y || m <= 0 || n <= 0 || k <= 0) return INT4L_ERR_INVALID_ARG;
+    if (k % 32 != 0 || k >= 131072) return INT4L_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15u)
+        return INT4L_ERR_MISALIGNED;
+    return INT4L_OK;
+}
+
+void report(int status, const char* what)
+{
+    t_last_status = status;
+    if (status != INT4L_OK)
+        std::fprintf(stderr, "CUDA FAILED: %s (%s)\n", int4_linear_status_string(status), what);
+}
+
+}  // namespace
+
+void count_launch(int n) { g_launches.fetch_add(n); }
+
+bool getenv_flag_direct_store()
+{
+    int v = g_direct_store.load();
+    if (v < 0) {
+        const char* e = std::getenv("INT4L_EPILOGUE");
+        v = (e && !std::strcmp(e, "direct")) ? 1 : 0;
+        g_direct_store.store(v);
+    }
+    return v != 0;
+}
+
+int forced_tile_n()
+{
+    int v = g_tile_n.load();
+    if (v == 0) {
+        const char* e = std::getenv("INT4L_TILE_N");
+        if (e) v = std::atoi(e);
+    }
+    return v;
+}
+
+DeviceCtx* current_ctx(int* status)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        *status = INT4L_ERR_NO_DEVICE;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceCtx* c = &g_ctx[dev];
+    if (g_ctx_ready[dev]) { *status = INT4L_OK; return c; }
+
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) { cudaGetLastError(); *status = INT4L_ERR_NO_DEVICE; return nullptr; }
+    if (prop.major != 10) { *status = INT4L_ERR_NO_DEVICE; return nullptr; }
+    c->device = dev;
+    c->sm_count = prop.multiProcessorCount;
+    c->cc_major = prop.major;
+    c->cc_minor = prop.minor;
+
+    void* host = nullptr;
+    if (cudaHostAlloc(&host, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) { *status = INT4L_ERR_CUDA; return nullptr; }
+    std::memset(host, 0, 64);
+    void* devp = nullptr;
+    if (cudaHostGetDevicePointer(&devp, host, 0) != cudaSuccess) { *status = INT4L_ERR_CUDA; return nullptr; }
+    c->status_host = static_cast<volatile int*>(host);
+    c->status_dev = static_cast<int*>(devp);
+
+    cudaDriverEntryPointQueryResult qres;
+    void* fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn) {
+        *status = INT4L_ERR_CUDA;
+        return nullptr;
+    }
+    c->encode_tiled = fn;
+
+    int rc = setup_tcgen05(c);
+    if (rc == INT4L_OK) rc = setup_skinny(c);
+    if (rc != INT4L_OK) { *status = rc; return nullptr; }
+    c->attrs_set = true;
+    g_ctx_ready[dev] = true;
+    *status = INT4L_OK;
+    return c;
+}
+
+int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int elem_bytes,
+                       uint64_t inner_elems, uint64_t rows, uint64_t row_pitch_bytes,
+                       uint32_t box_inner, uint32_t box_rows, bool swizzle128)
+{
+    const cuuint64_t dims[2] = {inner_elems, rows};
+    const cuuint64_t strides[1] = {row_pitch_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+        out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+bool skinny_supports(const DeviceCtx* ctx, const Problem& p);
+
+namespace {
+
+int choose_path(const DeviceCtx* ctx, const Problem& p)
+{
+    const int forced = current_path();
+    if (forced == INT4L_PATH_SKINNY) return skinny_supports(ctx, p) ? INT4L_PATH_SKINNY : INT4L_PATH_TCGEN05;
+    if (forced != INT4L_PATH_AUTO) return forced;
+    if (skinny_supports(ctx, p)) return INT4L_PATH_SKINNY;
+    return INT4L_PATH_TCGEN05;
+}
+
+int dispatch(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
+{
+    switch (choose_path(ctx, p)) {
+        case INT4L_PATH_SKINNY: return launch_skinny(ctx, p, stream);
+        case INT4L_PATH_LEGACY: return launch_legacy(ctx, p, stream);
+        default: return launch_tcgen05(ctx, p, stream);
+    }
+}
+
+int poll_device_status(DeviceCtx* ctx)
+{
+    if (!ctx || !ctx->status_host) return INT4L_OK;
+    int s = *ctx->status_host;
+    if (s != INT4L_OK) *ctx->status_host = INT4L_OK;
+    return s;
+}
+
+int ensure_stage(void** buf, size_t* have, size_t need)
+{
+    if (*have >= need) return INT4L_OK;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    if (cudaMalloc(buf, need) != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+    *have = need;
+    return INT4L_OK;
+}
+
+}  // namespace
+
+}  // namespace i4l
+
+using namespace i4l;
+
+extern "C" {
+
+int int4_linear_launch_async(const void* x, const void* w, void* y, int m, int n, int k, void* stream)
+{
+    int rc = check_args(x, w, y, m, n, k);
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{x, w, y, m, n, k};
+    rc = dispatch(ctx, p, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
+void int4_linear_launch(void* x, void* w, void* y, int m, int n, int k)
+{
+    int rc = int4_linear_launch_async(x, w, y, m, n, k, nullptr);
+    if (rc != INT4L_OK) { report(rc, "launch"); return; }
+    if (cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); report(INT4L_ERR_CUDA, "synchronize"); return; }
+    int st = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&st);
+    st = poll_device_status(ctx);
+    report(st, "kernel");
+}
+
+int int4_linear_host(const void* x_h, const void* w_h, void* y_h, int m, int n, int k, int w_resident)
+{
+    int rc = check_args(x_h, w_h, y_h, m, n, k);
+    if (rc == INT4L_ERR_MISALIGNED) rc = INT4L_OK;  // host buffers need no alignment
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    const size_t xb = static_cast<size_t>(m) * k / 2, wb = static_cast<size_t>(n) * k / 2;
+    const size_t yb = static_cast<size_t>(m) * n * 4;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        const bool w_buf_grew = ctx->stage_w_bytes < wb;
+        rc = ensure_stage(&ctx->stage_x, &ctx->stage_x_bytes, xb);
+        if (rc == INT4L_OK) rc = ensure_stage(&ctx->stage_w, &ctx->stage_w_bytes, wb);
+        if (rc == INT4L_OK) rc = ensure_stage(&ctx->stage_y, &ctx->stage_y_bytes, yb);
+        if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+        const bool reuse = w_resident && !w_buf_grew && ctx->stage_w_src == w_h && ctx->stage_w_src_bytes == wb;
+        cudaError_t e = cudaMemcpyAsync(ctx->stage_x, x_h, xb, cudaMemcpyHostToDevice, nullptr);
+        if (e == cudaSuccess && !reuse) {
+            e = cudaMemcpyAsync(ctx->stage_w, w_h, wb, cudaMemcpyHostToDevice, nullptr);
+            ctx->stage_w_src = w_h;
+            ctx->stage_w_src_bytes = wb;
+        }
+        if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
+        Problem p{ctx->stage_x, ctx->stage_w, ctx->stage_y, m, n, k};
+        rc = dispatch(ctx, p, nullptr);
+        if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+        e = cudaMemcpyAsync(y_h, ctx->stage_y, yb, cudaMemcpyDeviceToHost, nullptr);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+        if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
+    }
+    rc = poll_device_status(ctx);
+    t_last_status = rc;
+    return rc;
+}
+
+int int4_linear_last_status(void)
+{
+    int st = INT4L_OK;
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_ctx_ready[dev])
+        st = poll_device_status(&g_ctx[dev]);
+    else
+        cudaGetLastError();
+    if (st != INT4L_OK) t_last_status = st;
+    return t_last_status;
+}
+
+const char* int4_linear_status_string(int status)
+{
+    switch (status) {
+        case INT4L_OK: return "ok";
+        case INT4L_ERR_INVALID_ARG: return "invalid argument";
+        case INT4L_ERR_UNSUPPORTED: return "unsupported shape (need k % 32 == 0 and k < 131072)";
+        case INT4L_ERR_MISALIGNED: return "pointer not 16-byte aligned";
+        case INT4L_ERR_CUDA: return "CUDA call failed";
+        case INT4L_ERR_DEVICE_TIMEOUT: return "in-kernel wait timed out";
+        case INT4L_ERR_NO_DEVICE: return "no sm_100 device";
+        case INT4L_ERR_TOO_LARGE: return "size beyond the fixed capacity of this entry point";
+        default: return "unknown status";
+    }
+}
+
+int int4_linear_set_path(int path)
+{
+    int prev = current_path();
+    if (path >= INT4L_PATH_AUTO && path <= INT4L_PATH_SKINNY) g_path.store(path);
+    return prev;
+}
+
+int int4_linear_set_tuning(int tile_n, int direct_store)
+{
+    if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return INT4L_ERR_INVALID_ARG;
+    g_tile_n.store(tile_n);
+    g_direct_store.store(direct_store ? 1 : 0);
+    return INT4L_OK;
+}
+
+int int4_linear_path_for(int m, int n, int k)
+{
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) return -rc;
+    Problem p{nullptr, nullptr, nullptr, m, n, k};
+    return choose_path(ctx, p);
+}
+
+long long int4_linear_launch_count(void) { return g_launches.load(); }
+
+int int4_linear_version(void) { return 100; }
+
+}  // extern "C"
+
+// The reference declares its launcher with C++ linkage (kernels/linear_v21.h:760);
+// exporting the same symbol lets test/test_correctness.cu link against this
+// library unchanged.
+void linear_v21_launch(void* x_packed_d, void* w_packed_d, void* y_d, int m, int n, int k)
+{
+    int4_linear_launch(x_packed_d, w_packed_d, y_d, m, n, k);
+}

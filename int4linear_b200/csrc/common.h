@@ -1,0 +1,72 @@
+// Internal declarations shared by the kernels and the C-ABI layer.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/int4linear_b200.h"
+
+namespace i4l {
+
+// Problem description handed to every kernel launcher.  Operand format is the
+// reference's (kernels/linear_v21.h:62-69): X is M x K and W is N x K, both
+// packed two signed nibbles per byte (low nibble = even index) with a row
+// pitch of K/2 bytes; Y is M x N int32, row-major.
+struct Problem {
+    const void* x;
+    const void* w;
+    void* y;
+    int m, n, k;
+};
+
+// Per-device state created on the first call on that device.
+struct DeviceCtx {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    // Host-mapped word the kernels raise when a bounded wait expires.
+    volatile int* status_host = nullptr;
+    int* status_dev = nullptr;
+    // cuTensorMapEncodeTiled, resolved through the runtime (no libcuda link).
+    void* encode_tiled = nullptr;
+    // Device scratch owned by the host-buffer entry point.
+    void* stage_x = nullptr; size_t stage_x_bytes = 0;
+    void* stage_w = nullptr; size_t stage_w_bytes = 0;
+    void* stage_y = nullptr; size_t stage_y_bytes = 0;
+    const void* stage_w_src = nullptr;  // host weights currently resident in stage_w
+    size_t stage_w_src_bytes = 0;
+    bool attrs_set = false;
+};
+
+// Returns the context of the current device (nullptr + status on failure).
+DeviceCtx* current_ctx(int* status);
+
+// Builds a 2-D tiled tensor map over a row-major byte/word matrix.
+//   elem_bytes 1 -> UINT8 elements, 4 -> INT32 elements.
+//   swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (inner box must be 128 B).
+int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int elem_bytes,
+                       uint64_t inner_elems, uint64_t rows, uint64_t row_pitch_bytes,
+                       uint32_t box_inner, uint32_t box_rows, bool swizzle128);
+
+// Kernel launchers.  Each returns an INT4L_* status; none of them synchronises.
+int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+int launch_legacy(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+
+// One-off function attribute set-up (dynamic shared memory opt-in).
+int setup_tcgen05(DeviceCtx* ctx);
+int setup_skinny(DeviceCtx* ctx);
+
+// Launch counter (kernels of this library launched by this process).
+void count_launch(int n = 1);
+
+// True when the decode-shape kernel can run this problem (m <= 64 and X fits
+// in shared memory).
+bool skinny_supports(const DeviceCtx* ctx, const Problem& p);
+
+// Experiment knobs (int4_linear_set_tuning / INT4L_EPILOGUE, INT4L_TILE_N).
+bool getenv_flag_direct_store();
+int forced_tile_n();
+
+}  // namespace i4l

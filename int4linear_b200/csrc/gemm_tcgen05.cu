@@ -1,0 +1,361 @@
+// Main GEMM kernel: packed s4 operands -> TMA -> shared-memory ring ->
+// in-smem s4->s8 unpack -> tcgen05.mma kind::i8 (int32 accumulators in tensor
+// memory) -> TMEM->register->(smem->TMA store | direct store) epilogue.
+//
+// Replaces the device side of the reference's kernels/linear_v21.h:471-753
+// (cp.async ring, XOR swizzle, ldmatrix, mma.sync m16n8k64, int2 stores).
+//
+// Work decomposition
+//   One persistent CTA per SM walks output tiles of 128 x BN.  K advances in
+//   blocks of 128 elements (64 packed bytes per row).
+//   Warp roles (448 threads):
+//     warp 0      TMA producer: packed X tile (128 x 64 B) and W tile (BN x 64 B)
+//                 per K block into the "packed" ring; OOB rows/bytes read as 0,
+//                 which implements every M, N and K tail.
+//     warps 6-13  unpack: read the packed ring, expand nibbles to bytes, write
+//                 the "unpacked" ring in the UMMA K-major 128-byte-swizzled
+//                 layout, release the packed slot.
+//     warp 1      UMMA issuer: four 128 x BN x 32 tcgen05.mma per K block into one
+//                 of two TMEM accumulator buffers; tcgen05.commit releases the
+//                 unpacked slot / publishes the finished accumulator.
+//     warps 2-5   epilogue: tcgen05.ld the accumulator (one TMEM sub-partition of
+//                 32 lanes each), undo the scaling, write Y.  Overlaps the next
+//                 tile's main loop through the second accumulator buffer.
+//
+// The unpack
+//   A packed 32-bit word x holds nibbles e0..e7.  (x << 4) & 0xF0F0F0F0 is four
+//   bytes equal to 16*e0, 16*e2, 16*e4, 16*e6 as signed 8-bit values, and
+//   x & 0xF0F0F0F0 is 16*e1, 16*e3, 16*e5, 16*e7: three ALU operations for
+//   eight elements, sign handled for free (-8 -> -128).  Even and odd elements
+//   end up de-interleaved, i.e. K is permuted inside each 32-element group;
+//   X and W go through the same permutation, and a dot product does not care
+//   in which order K is summed.  The accumulator is therefore exactly
+//   256 * y, and the epilogue shifts it right by 8 (arithmetic, exact).
+//   |256 * y| <= 256 * 64 * K < 2^31 needs K < 131072.
+#include "common.h"
+#include "ptx.cuh"
+
+namespace i4l {
+
+namespace {
+
+constexpr int kBM = 128;          // tile rows (UMMA M)
+constexpr int kBKBytes = 64;      // packed bytes per row per K block (128 elements)
+constexpr int kUnpackWarps = 8;
+constexpr int kThreads = 32 * (2 + 4 + kUnpackWarps);
+constexpr int kStoreStageBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+
+template <int BN, int P, int U>
+struct Cfg {
+    static constexpr int kBN = BN;
+    static constexpr int kP = P;
+    static constexpr int kU = U;
+    static constexpr int kPkStage = (kBM + BN) * kBKBytes;       // packed X then packed W
+    static constexpr int kUpStage = (kBM + BN) * 2 * kBKBytes;   // s8 X (16 KB) then s8 W
+    static constexpr int kTmemCols = 2 * BN;                     // two accumulator buffers
+    static constexpr int kNumBarriers = 2 * P + 2 * U + 4;
+    static constexpr int kSmemBytes = 1024 /*alignment slack*/ + U * kUpStage + P * kPkStage +
+                                      kStoreStageBytes + kNumBarriers * 8 + 16;
+    static_assert(((kBM + BN) * 4) % (kUnpackWarps * 32) == 0, "unpack loop must divide evenly");
+    static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns: power of two");
+};
+
+template <class C, bool kTmaStore>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
+                       const __grid_constant__ CUtensorMap tm_w,
+                       const __grid_constant__ CUtensorMap tm_y,
+                       int* __restrict__ y, int m, int n, int k,
+                       int tiles_m, int tiles_n, int* status)
+{
+    constexpr int BN = C::kBN, P = C::kP, U = C::kU;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - raw);
+
+    const uint32_t up_base = base;
+    const uint32_t pk_base = up_base + U * C::kUpStage;
+    const uint32_t st_base = pk_base + P * C::kPkStage;
+    const uint32_t bar_base = st_base + kStoreStageBytes;
+    auto pk_full  = [&](int i) { return bar_base + 8u * i; };
+    auto pk_empty = [&](int i) { return bar_base + 8u * (P + i); };
+    auto up_full  = [&](int i) { return bar_base + 8u * (2 * P + i); };
+    auto up_empty = [&](int i) { return bar_base + 8u * (2 * P + U + i); };
+    auto tm_full  = [&](int i) { return bar_base + 8u * (2 * P + 2 * U + i); };
+    auto tm_empty = [&](int i) { return bar_base + 8u * (2 * P + 2 * U + 2 + i); };
+    const uint32_t misc_off = (bar_base - base) + 8u * C::kNumBarriers;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + misc_off + 4);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < P; ++i) { mbar_init(pk_full(i), 1); mbar_init(pk_empty(i), kUnpackWarps); }
+        for (int i = 0; i < U; ++i) { mbar_init(up_full(i), kUnpackWarps); mbar_init(up_empty(i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tm_full(i), 1); mbar_init(tm_empty(i), 4); }
+        *abort_flag = 0;
+        mbar_init_fence();
+        tma_prefetch_desc(&tm_x);
+        tma_prefetch_desc(&tm_w);
+        if (kTmaStore) tma_prefetch_desc(&tm_y);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = tiles_m * tiles_n;
+    const int kb_count = (k + 127) / 128;
+    constexpr int kGroupM = 16;  // tiles of 16 consecutive M blocks share their W panel in L2
+    auto tile_coord = [&](int tile, int& tm, int& tn) {
+        const int group_size = kGroupM * tiles_n;
+        const int group = tile / group_size;
+        const int first_m = group * kGroupM;
+        const int gm = min(tiles_m - first_m, kGroupM);
+        const int in_group = tile - group * group_size;
+        tm = first_m + in_group % gm;
+        tn = in_group / gm;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x) {
+                int tm, tn;
+                tile_coord(tile, tm, tn);
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const uint32_t s = it % P, r = it / P;
+                    if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                    mbar_expect_tx(pk_full(s), C::kPkStage);
+                    const uint32_t dst = pk_base + s * C::kPkStage;
+                    tma_load_2d(dst, &tm_x, pk_full(s), kb * kBKBytes, tm * kBM);
+                    tma_load_2d(dst + kBM * kBKBytes, &tm_w, pk_full(s), kb * kBKBytes, tn * BN);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------- UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_s8(kBM, BN);
+            uint32_t it = 0, local_tile = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+                const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
+                if (!mbar_wait(tm_empty(buf), (br & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                    const uint32_t s = it % U, r = it / U;
+                    if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = up_base + s * C::kUpStage;
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(a_addr + kBM * 128);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // 32 bytes of K per instruction: advance the start address field by 32 >> 4.
+                        umma_i8<1>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(up_empty(s));
+                }
+                if (alive) umma_commit(tm_full(buf));
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // ---------------------------------------------------------- epilogue
+        const int sp = warp & 3;  // TMEM sub-partition this warp may read
+        const uint32_t stage0 = st_base + (warp - 2) * 8192;
+        const bool vec_ok = (n & 3) == 0;
+        uint32_t local_tile = 0;
+        uint32_t chunk_no = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            int tm, tn;
+            tile_coord(tile, tm, tn);
+            const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
+            if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
+            tc_fence_after_sync();
+            const int row0 = tm * kBM + sp * 32;
+            const int row = row0 + lane;
+            const int col0 = tn * BN;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32, ++chunk_no) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_addr + c, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = static_cast<uint32_t>(static_cast<int>(v[i]) >> 8);
+                if constexpr (kTmaStore) {
+                    const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
+                    // The store issued two chunks ago read this buffer; make sure it is done.
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        sts128(stg + lane * 128 + ((q ^ (lane & 7)) << 4),
+                               make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < m && col0 + c < n) {
+                        tma_store_2d(&tm_y, stg, col0 + c, row0);
+                        tma_store_commit();
+                    }
+                } else {
+                    if (row < m) {
+                        int* dst = y + static_cast<size_t>(row) * n + col0 + c;
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int col = col0 + c + 4 * q;
+                            if (vec_ok && col + 3 < n) {
+                                *reinterpret_cast<int4*>(dst + 4 * q) =
+                                    make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (col + e < n) dst[4 * q + e] = static_cast<int>(v[4 * q + e]);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tm_empty(buf));
+        }
+        if (kTmaStore && lane == 0) tma_store_wait_all<0>();
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ unpack
+        const int utid = tid - 6 * 32;  // 0 .. 255
+        constexpr int kChunks = (kBM + BN) * 4;  // 16-byte packed chunks per stage
+        uint32_t it = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x) {
+            for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                const uint32_t ps = it % P, pr = it / P;
+                const uint32_t us = it % U, ur = it / U;
+                if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
+                if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                const uint32_t src = pk_base + ps * C::kPkStage;
+                const uint32_t dst = up_base + us * C::kUpStage;
+#pragma unroll
+                for (int i = 0; i < kChunks / 256; ++i) {
+                    const int q = i * 256 + utid;
+                    const int r = q >> 2, c = q & 3;
+                    const uint4 x = lds128(src + q * 16);
+                    uint4 lo, hi;
+                    lo.x = (x.x << 4) & 0xF0F0F0F0u; hi.x = x.x & 0xF0F0F0F0u;
+                    lo.y = (x.y << 4) & 0xF0F0F0F0u; hi.y = x.y & 0xF0F0F0F0u;
+                    lo.z = (x.z << 4) & 0xF0F0F0F0u; hi.z = x.z & 0xF0F0F0F0u;
+                    lo.w = (x.w << 4) & 0xF0F0F0F0u; hi.w = x.w & 0xF0F0F0F0u;
+                    const uint32_t rowaddr = dst + r * 128;
+                    const uint32_t sw = r & 7;
+                    sts128(rowaddr + (((2 * c) ^ sw) << 4), lo);
+                    sts128(rowaddr + (((2 * c + 1) ^ sw) << 4), hi);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(up_full(us));
+                    mbar_arrive(pk_empty(ps));
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        // Something never arrived.  Report, give copies in flight time to land,
+        // then release tensor memory so the SM stays usable.
+        if (tid == 0) atomicExch(status, INT4L_ERR_DEVICE_TIMEOUT);
+        for (int i = 0; i < 100; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, C::kTmemCols);
+    }
+}
+
+using Cfg256 = Cfg<256, 3, 2>;
+using Cfg128 = Cfg<128, 4, 3>;
+using Cfg64 = Cfg<64, 4, 4>;
+
+template <class C, bool kTmaStore>
+int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
+{
+    const int tiles_m = (p.m + kBM - 1) / kBM;
+    const int tiles_n = (p.n + C::kBN - 1) / C::kBN;
+    const uint64_t pitch = static_cast<uint64_t>(p.k) / 2;
+    CUtensorMap tm_x, tm_w, tm_y;
+    int rc = make_tensor_map_2d(ctx, &tm_x, p.x, 1, pitch, p.m, pitch, kBKBytes, kBM, false);
+    if (rc != INT4L_OK) return rc;
+    rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kBN, false);
+    if (rc != INT4L_OK) return rc;
+    if (kTmaStore) {
+        rc = make_tensor_map_2d(ctx, &tm_y, p.y, 4, p.n, p.m, static_cast<uint64_t>(p.n) * 4, 32, 32, true);
+        if (rc != INT4L_OK) return rc;
+    } else {
+        tm_y = tm_x;  // unused by the kernel
+    }
+    const int grid = min(tiles_m * tiles_n, ctx->sm_count);
+    gemm_s4_tcgen05_kernel<C, kTmaStore><<<grid, kThreads, C::kSmemBytes, stream>>>(
+        tm_x, tm_w, tm_y, static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, ctx->status_dev);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+template <class C>
+int set_attr()
+{
+    cudaError_t e = cudaFuncSetAttribute(gemm_s4_tcgen05_kernel<C, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return INT4L_ERR_CUDA;
+    e = cudaFuncSetAttribute(gemm_s4_tcgen05_kernel<C, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    return e == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+}  // namespace
+
+int setup_tcgen05(DeviceCtx*)
+{
+    int rc = set_attr<Cfg256>();
+    if (rc == INT4L_OK) rc = set_attr<Cfg128>();
+    if (rc == INT4L_OK) rc = set_attr<Cfg64>();
+    return rc;
+}
+
+// Tile-width choice: the widest N tile that still yields at least one tile per
+// SM, because a wide tile re-reads X less often but a grid smaller than the
+// machine leaves SMs idle.
+int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
+{
+    const bool tma_store = (p.n % 4 == 0) && !getenv_flag_direct_store();
+    const long long tiles_m = (p.m + kBM - 1) / kBM;
+    auto tiles = [&](int bn) { return tiles_m * ((p.n + bn - 1) / bn); };
+    int bn = 256;
+    if (tiles(256) < ctx->sm_count) bn = 128;
+    if (bn == 128 && tiles(128) < ctx->sm_count) bn = 64;
+    const int forced = forced_tile_n();
+    if (forced == 64 || forced == 128 || forced == 256) bn = forced;
+    if (bn == 256) return tma_store ? launch_cfg<Cfg256, true>(ctx, p, stream) : launch_cfg<Cfg256, false>(ctx, p, stream);
+    if (bn == 128) return tma_store ? launch_cfg<Cfg128, true>(ctx, p, stream) : launch_cfg<Cfg128, false>(ctx, p, stream);
+    return tma_store ? launch_cfg<Cfg64, true>(ctx, p, stream) : launch_cfg<Cfg64, false>(ctx, p, stream);
+}
+
+}  // namespace i4l

@@ -1,0 +1,152 @@
+"""Host-side mirror of the reference's launcher interface.
+
+Reference                                   here
+------------------------------------------  ---------------------------------
+struct LinearArgs {X_ptr, W_ptr, Y_ptr,     LinearArgs (same field names/order)
+  m, n, k}      kernels/linear_v21.h:62-69
+void linear_v21_launch(x_packed_d,          linear_v21_launch(...) -- device
+  w_packed_d, y_d, m, n, k)                   pointers or CUDA tensors, blocking,
+                kernels/linear_v21.h:760      result complete on return
+main() of test/test_correctness.cu:53-63    linear_host(...) -- host arrays in,
+  (malloc/H2D/launch/D2H)                     host array out
+
+`linear` is the convenience form for CUDA tensors.  All of them end in the
+C ABI of libint4linear_b200.so; none computes anything on the CPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+
+PATH_AUTO, PATH_TCGEN05, PATH_LEGACY, PATH_SKINNY = 0, 1, 2, 3
+
+
+class Int4LinearError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = _lib.load().int4_linear_status_string(status).decode()
+        super().__init__(f"{where}: {msg} (status {status})")
+
+
+@dataclass
+class LinearArgs:
+    """Field-for-field the reference's kernel argument block (kernels/linear_v21.h:62-69)."""
+    X_ptr: int
+    W_ptr: int
+    Y_ptr: int
+    m: int
+    n: int
+    k: int
+
+
+def _ptr(t) -> int:
+    if isinstance(t, int):
+        return t
+    if hasattr(t, "data_ptr"):
+        if not t.is_cuda:
+            raise ValueError("expected a CUDA tensor (device pointer)")
+        if not t.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return t.data_ptr()
+    raise TypeError(f"cannot take a device pointer from {type(t)!r}")
+
+
+def linear_v21_launch(x_packed_d, w_packed_d, y_d, m: int, n: int, k: int) -> None:
+    """Blocking launch on the current device's default stream, as the reference's
+    launcher.  Arguments are device pointers (ints) or CUDA tensors.  Unlike the
+    reference, which returns nothing and prints only in debug builds, a failure
+    raises Int4LinearError."""
+    lib = _lib.load()
+    lib.int4_linear_launch(_ptr(x_packed_d), _ptr(w_packed_d), _ptr(y_d), m, n, k)
+    st = lib.int4_linear_last_status()
+    if st != 0:
+        raise Int4LinearError(st, "linear_v21_launch")
+
+
+def launch(args: LinearArgs, stream=None) -> None:
+    """Asynchronous launch from a LinearArgs block on `stream` (a torch.cuda.Stream,
+    a raw cudaStream_t handle, or None for the current torch stream)."""
+    import torch
+    lib = _lib.load()
+    if stream is None:
+        handle = torch.cuda.current_stream().cuda_stream
+    elif hasattr(stream, "cuda_stream"):
+        handle = stream.cuda_stream
+    else:
+        handle = int(stream)
+    st = lib.int4_linear_launch_async(args.X_ptr, args.W_ptr, args.Y_ptr, args.m, args.n, args.k, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_launch_async")
+
+
+def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None):
+    """Y = X @ W^T for packed CUDA tensors.
+
+    x_packed: [m, k/2] uint8 (or [m, k/8] int32) on a B200; w_packed likewise with n rows.
+    Returns an [m, n] int32 CUDA tensor (written into `out` when given).  Asynchronous
+    on the current torch stream; call last_status() after a synchronize to learn
+    about device-side failures."""
+    import torch
+    if not (x_packed.is_cuda and w_packed.is_cuda):
+        raise ValueError("linear() needs CUDA tensors; there is no CPU implementation")
+    xb = x_packed.contiguous().view(torch.uint8)
+    wb = w_packed.contiguous().view(torch.uint8)
+    m, n = xb.shape[0], wb.shape[0]
+    if k is None:
+        k = xb.shape[1] * 2
+    if xb.shape[1] * 2 != k or wb.shape[1] * 2 != k:
+        raise ValueError("packed widths do not match k")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.int32, device=xb.device)
+    with torch.cuda.device(xb.device):
+        launch(LinearArgs(xb.data_ptr(), wb.data_ptr(), out.data_ptr(), m, n, k), stream)
+    return out
+
+
+def linear_host(x_packed: np.ndarray, w_packed: np.ndarray, k: int, out: np.ndarray | None = None,
+                w_resident: bool = False) -> np.ndarray:
+    """The whole host-side sequence of the reference's correctness program
+    (allocate, upload, launch, download; test/test_correctness.cu:53-63) for
+    operands in host memory.  Returns (and fills) an [m, n] int32 numpy array."""
+    x_packed = np.ascontiguousarray(x_packed)
+    w_packed = np.ascontiguousarray(w_packed)
+    m, n = x_packed.shape[0], w_packed.shape[0]
+    if x_packed.nbytes != m * k // 2 or w_packed.nbytes != n * k // 2:
+        raise ValueError("packed sizes do not match k")
+    if out is None:
+        out = np.empty((m, n), dtype=np.int32)
+    st = _lib.load().int4_linear_host(x_packed.ctypes.data, w_packed.ctypes.data, out.ctypes.data,
+                                      m, n, k, 1 if w_resident else 0)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_host")
+    return out
+
+
+def last_status() -> int:
+    return _lib.load().int4_linear_last_status()
+
+
+def launch_count() -> int:
+    return _lib.load().int4_linear_launch_count()
+
+
+def set_path(path: int) -> int:
+    return _lib.load().int4_linear_set_path(path)
+
+
+def set_tuning(tile_n: int = 0, direct_store: bool = False) -> None:
+    st = _lib.load().int4_linear_set_tuning(tile_n, 1 if direct_store else 0)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_set_tuning")
+
+
+def path_for(m: int, n: int, k: int) -> int:
+    r = _lib.load().int4_linear_path_for(m, n, k)
+    if r < 0:
+        raise Int4LinearError(-r, "int4_linear_path_for")
+    return r

@@ -1,0 +1,144 @@
+"""GPU: bit-exact parity of every kernel family with the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+import int4linear_b200 as L
+from conftest import golden_files, make_case
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False):
+    """Upload packed operands, run one blocking launch through the C ABI, download Y."""
+    import torch
+    xd = torch.from_numpy(xp).to(cuda)
+    wd = torch.from_numpy(wp).to(cuda)
+    m, n = xp.shape[0], wp.shape[0]
+    yd = torch.full((m, n), -12345, dtype=torch.int32, device=cuda)
+    prev = L.set_path(path)
+    L.set_tuning(tile_n, direct)
+    try:
+        L.linear_v21_launch(xd, wd, yd, m, n, k)
+    finally:
+        L.set_path(prev)
+        L.set_tuning(0, False)
+    return yd.cpu().numpy()
+
+
+VARIANTS = [
+    ("tcgen05-256-tma", dict(path=L.PATH_TCGEN05, tile_n=256, direct=False)),
+    ("tcgen05-256-direct", dict(path=L.PATH_TCGEN05, tile_n=256, direct=True)),
+    ("tcgen05-128-tma", dict(path=L.PATH_TCGEN05, tile_n=128, direct=False)),
+    ("tcgen05-64-direct", dict(path=L.PATH_TCGEN05, tile_n=64, direct=True)),
+    ("legacy", dict(path=L.PATH_LEGACY)),
+    ("auto", dict(path=L.PATH_AUTO)),
+]
+
+
+@pytest.mark.parametrize("vname,variant", VARIANTS, ids=[v[0] for v in VARIANTS])
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: p.split("/")[-1][:-4])
+def test_golden_vectors(cuda, path, vname, variant):
+    g = np.load(path)
+    k = g["x"].shape[1]
+    if k % 32:
+        pytest.skip("k % 32 != 0 is outside the device contract")
+    xp = g["x_packed"].view(np.uint8).reshape(g["x"].shape[0], -1)
+    wp = g["w_packed"].view(np.uint8).reshape(g["w"].shape[0], -1)
+    y = run_device(cuda, xp, wp, k, **variant)
+    assert O.is_same(y, g["y"])
+
+
+# (m, n, k): M/N/K tails around every tile size, the reference's edge cases
+# (rows predicated at tile edges, K tail at 32-element granularity) and odd N.
+TAIL_SHAPES = [
+    (1, 2, 32), (16, 130, 96), (17, 14, 128), (255, 258, 160), (257, 130, 32),
+    (128, 256, 128), (129, 257, 224), (300, 77, 416), (64, 1000, 1056), (384, 512, 2048),
+]
+
+
+@pytest.mark.parametrize("vname,variant", VARIANTS, ids=[v[0] for v in VARIANTS])
+@pytest.mark.parametrize("shape", TAIL_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_tail_shapes(cuda, shape, vname, variant):
+    m, n, k = shape
+    x, w, xp, wp = make_case(m, n, k, seed=m + n + k)
+    y = run_device(cuda, xp, wp, k, **variant)
+    ref = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+    assert O.is_same(y, ref)
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 32), (16, 14336, 4096), (7, 100, 992), (32, 520, 1024), (64, 264, 2048), (48, 8, 128)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_skinny_kernel(cuda, shape):
+    m, n, k = shape
+    x, w, xp, wp = make_case(m, n, k, seed=9)
+    assert L.path_for(m, n, k) == L.PATH_SKINNY
+    y = run_device(cuda, xp, wp, k, path=L.PATH_SKINNY)
+    ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+    assert O.is_same(y, ref)
+    # the tensor-memory family must agree on the same inputs
+    y2 = run_device(cuda, xp, wp, k, path=L.PATH_TCGEN05)
+    assert O.is_same(y2, ref)
+
+
+def test_extreme_values_closed_form(cuda):
+    """All -8 times all -8 is the largest accumulator the format can produce: 64*K per element."""
+    for k in (128, 8192, 65536):
+        m, n = 130, 72
+        xp = np.full((m, k // 2), 0x88, dtype=np.uint8)
+        wp = np.full((n, k // 2), 0x88, dtype=np.uint8)
+        for path in (L.PATH_TCGEN05, L.PATH_LEGACY):
+            y = run_device(cuda, xp, wp, k, path=path)
+            assert (y == 64 * k).all()
+        wp7 = np.full((n, k // 2), 0x77, dtype=np.uint8)
+        y = run_device(cuda, xp, wp7, k, path=L.PATH_TCGEN05)
+        assert (y == -56 * k).all()
+
+
+def test_single_nonzero_positions(cuda):
+    """One non-zero per row at varying K positions: any K permutation that differs between
+    the operands, or a swizzle slip, shows up as a wrong or missing product."""
+    m, n, k = 128, 256, 512
+    x = np.zeros((m, k), np.int8)
+    w = np.zeros((n, k), np.int8)
+    for i in range(m):
+        x[i, (37 * i + 11) % k] = (i % 15) - 7 or 3
+    for j in range(n):
+        w[j, (37 * j + 11) % k] = -8 if j % 2 else 7
+    ref = x.astype(np.int32) @ w.astype(np.int32).T
+    for path in (L.PATH_TCGEN05, L.PATH_LEGACY):
+        y = run_device(cuda, L.pack_bytes(x), L.pack_bytes(w), k, path=path)
+        assert O.is_same(y, ref)
+
+
+def test_repeatable(cuda):
+    """Integer arithmetic: two runs must agree bit for bit, anything else is a race."""
+    m, n, k = 512, 768, 1024
+    x, w, xp, wp = make_case(m, n, k, seed=4)
+    a = run_device(cuda, xp, wp, k)
+    b = run_device(cuda, xp, wp, k)
+    assert O.is_same(a, b)
+
+
+def test_host_buffer_entry_point(cuda):
+    m, n, k = 100, 300, 256
+    x, w, xp, wp = make_case(m, n, k, seed=2)
+    ref = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+    before = L.launch_count()
+    y = L.linear_host(xp, wp, k)
+    assert O.is_same(y, ref)
+    # weights declared resident: same result without re-uploading them
+    x2 = L.uniform_s4(77, m, k)
+    y2 = L.linear_host(L.pack_bytes(x2), wp, k, w_resident=True)
+    assert O.is_same(y2, O.linear_ref(x2.astype(np.int32), w.astype(np.int32)))
+    assert L.launch_count() == before + 2
+
+
+def test_tensor_front_end(cuda):
+    import torch
+    m, n, k = 96, 160, 384
+    x, w, xp, wp = make_case(m, n, k, seed=6)
+    y = L.linear(torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda))
+    torch.cuda.synchronize()
+    assert L.last_status() == 0
+    assert O.is_same(y.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))

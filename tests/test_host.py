@@ -1,0 +1,84 @@
+"""CPU: packer, generator, library loading, argument checking (no GPU needed)."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+import int4linear_b200 as L
+from int4linear_b200 import _lib
+from conftest import ROOT, golden_files
+from oracle import oracle as O
+
+
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: p.split("/")[-1][:-4])
+def test_packer_matches_golden(path):
+    g = np.load(path)
+    x = g["x"].astype(np.int32)
+    assert np.array_equal(L.pack(x), g["x_packed"])
+    assert np.array_equal(L.unpack(g["x_packed"], x.shape[1]), x)
+    if x.shape[1] % 8 == 0:
+        as_bytes = g["x_packed"].view(np.uint8).reshape(x.shape[0], -1)
+        assert np.array_equal(L.pack_bytes(g["x"]), as_bytes)
+        assert np.array_equal(L.unpack_bytes(as_bytes), g["x"])
+
+
+def test_pack_roundtrip_all_values():
+    v = np.arange(-8, 8, dtype=np.int32).reshape(1, 16)
+    p = L.pack(v)
+    assert p.view(np.uint8).ravel()[0] == 0x98  # -8 in the low nibble, -7 in the high one
+    assert np.array_equal(L.unpack(p, 16), v)
+    assert np.array_equal(O.unpack(p, 16), v)
+
+
+def test_generator_is_counter_based_and_uniform():
+    a = L.uniform_s4(42, 64, 256)
+    assert a.min() == -8 and a.max() == 7
+    # any row range reproduces the same values
+    b = L.uniform_s4(42, 16, 256, row_start=20)
+    assert np.array_equal(a[20:36], b)
+    p = L.uniform_s4_packed(42, 64, 256, chunk_rows=7)
+    assert np.array_equal(p, L.pack_bytes(a))
+    ps = L.uniform_s4_packed(42, 8, 256, row_start=40)
+    assert np.array_equal(ps, p[40:48])
+    counts = np.bincount((L.uniform_s4(1, 512, 512) + 8).ravel(), minlength=16)
+    assert counts.min() > 0.9 * counts.mean() and counts.max() < 1.1 * counts.mean()
+    assert not np.array_equal(L.uniform_s4(1, 4, 64), L.uniform_s4(2, 4, 64))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "int4linear_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(int4_linear_\w+)\s*\(", header))
+    assert declared, "no declarations found in the header"
+    lib = _lib.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert declared == set(_lib.SYMBOLS), "ctypes table and header disagree"
+    assert lib.int4_linear_version() >= 100
+
+
+def test_argument_checks_need_no_gpu():
+    lib = _lib.load()
+    buf = np.zeros(4096, dtype=np.uint8)
+    base = buf.ctypes.data
+    base += (-base) % 16
+    ok = (base, base, base)
+    assert lib.int4_linear_launch_async(None, base, base, 8, 8, 32, None) == 1
+    assert lib.int4_linear_launch_async(*ok, 0, 8, 32, None) == 1
+    assert lib.int4_linear_launch_async(*ok, 8, 8, 48, None) == 2      # k % 32 != 0
+    assert lib.int4_linear_launch_async(*ok, 8, 8, 131072, None) == 2  # k too large
+    assert lib.int4_linear_launch_async(base + 4, base, base, 8, 8, 32, None) == 3
+    assert lib.int4_linear_status_string(2).decode().startswith("unsupported")
+    assert lib.int4_linear_set_tuning(100, 0) == 1
+    assert lib.int4_linear_set_tuning(0, 0) == 0
+
+
+def test_no_gpu_means_error_not_fallback():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    x = np.zeros((8, 16), dtype=np.uint8)
+    with pytest.raises(L.Int4LinearError) as e:
+        L.linear_host(x, x, 32)
+    assert e.value.status == 6
