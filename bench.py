@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the INT4 linear GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload m8|c1..c5]
+                    [--impl ours|reference] [--scaling weak|strong]
+
+One process per GPU (for N > 1 launch through torch.distributed.run); rank 0
+prints ONE JSON line.  A step is one launch of the operator on seeded synthetic
+operands (i.i.d. uniform [-8, 7], packed as the reference's utils/packer does).
+
+Metric: INT4 GEMM TOPS = 2*M*N*K / t (the formula of the reference's
+test/benchmark.cu:112-113), default workload M=N=K=8192.
+  value     device-timed (CUDA events), operands resident in HBM, L2 flushed
+            before every timed launch as test/benchmark.cu:93-96 does
+  e2e       same metric through the host-buffer C-ABI entry point: pinned host
+            operands up, launch, result down, every step
+  roofline  achieved TOPS of the kernel against 2 x the measured dense bf16
+            tensor rate (B200's int8 rate is twice its bf16 rate), or GB/s
+            against the measured HBM copy rate for the decode shape
+  cpu_baseline  the reference's own CPU GEMM on a bounded row sample
+
+With N > 1 ranks the weight matrix is sharded along N: every rank holds the
+full X and its own rows of W and produces its own columns of Y; no collective is
+on the data path.  --scaling weak (default) keeps the per-GPU shard at the
+workload's N, --scaling strong splits the workload's N across the ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (M, N, K, bound)
+    "c1": (1024, 1024, 1024, "tensor"),
+    "c2": (4096, 4096, 4096, "tensor"),
+    "c3": (4096, 4096, 8192, "tensor"),
+    "c4": (16, 14336, 4096, "hbm"),
+    "c5": (8192, 28672, 8192, "tensor"),
+    "m8": (8192, 8192, 8192, "tensor"),
+}
+NOMINAL_INT8_TOPS = 4500.0
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def ncu_traffic(workload):
+    """DRAM bytes per launch from the committed ncu capture, if one exists."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get(workload)
+    return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_sample(m, n, k, seconds_target=15.0):
+    """Times the reference's CPU GEMM (test/test_correctness.cu:12-19) on rows 0..R-1 of
+    the workload, R sized for about `seconds_target` seconds.  Uses the reference's own
+    compiled function when oracle/_ref is there (one call per thread on its own row
+    block, all host cores), else the C restatement with OpenMP."""
+    import ctypes
+    from concurrent.futures import ThreadPoolExecutor
+    from int4linear_b200 import uniform_s4
+    from oracle import oracle as O
+
+    cores = os.cpu_count() or 1
+    w = np.ascontiguousarray(uniform_s4(0xB008, n, k).astype(np.int32))
+    ref = O.ref_lib()
+    kind = "reference" if ref is not None else "port"
+
+    def run(rows_per_thread):
+        rows = rows_per_thread * cores
+        x = np.ascontiguousarray(uniform_s4(0xA008, rows, k).astype(np.int32))
+        y = np.empty((rows, n), dtype=np.int32)
+        t0 = time.perf_counter()
+        if ref is not None:
+            ip = ctypes.POINTER(ctypes.c_int)
+
+            def job(t):
+                xs, ys = x[t * rows_per_thread:(t + 1) * rows_per_thread], y[t * rows_per_thread:(t + 1) * rows_per_thread]
+                ref.ref_linear_ref(xs.ctypes.data_as(ip), w.ctypes.data_as(ip), ys.ctypes.data_as(ip),
+                                   rows_per_thread, n, k)
+            with ThreadPoolExecutor(cores) as ex:
+                list(ex.map(job, range(cores)))
+        else:
+            y[:] = O.linear_ref(x, w)
+        return rows, time.perf_counter() - t0
+
+    rows, dt = run(1)
+    per_row_block = dt
+    reps = max(1, min(int(seconds_target / max(per_row_block, 1e-3)), max(1, m // cores)))
+    if reps > 1:
+        rows, dt = run(reps)
+    tops = 2.0 * rows * n * k / dt / 1e12
+    return {"value": tops, "unit": "TOPS", "cores": cores, "kind": kind,
+            "sample": f"rows 0..{rows - 1} of M={m} (N={n}, K={k}), {rows // cores} rows per thread, {dt:.1f} s"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="m8", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of Y (N > 1)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    m, n_work, k, bound = WORKLOADS[args.workload]
+    metric = (f"INT4 GEMM TOPS at M={m} N={n_work} K={k}" if bound == "tensor"
+              else f"INT4 GEMM achieved HBM GB/s at M={m} N={n_work} K={k}")
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb = cpu_reference_sample(m, n_work, k, seconds_target=max(5.0, min(60.0, 4.0 * args.steps)))
+        line = {"impl": "reference", "metric": f"INT4 GEMM TOPS at M={m} N={n_work} K={k}", "value": cb["value"], "unit": "TOPS",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": None, "higher_is_better": True, "scaling": args.scaling,
+                "vs_baseline": None, "dtype": "s4 x s4 -> s32 (int32 arithmetic on the CPU)",
+                "data": "synthetic", "config": {"workload": f"{args.workload}: M={m} N={n_work} K={k}"},
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    import int4linear_b200 as L
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- shard of the weight matrix this rank owns
+    if args.scaling == "strong":
+        n_total = n_work
+        n_local = n_total // world
+    else:
+        n_local = n_work
+        n_total = n_work * world
+    row_start = rank * n_local
+    xp = L.uniform_s4_packed(0xA008, m, k)
+    wp = L.uniform_s4_packed(0xB008, n_local, k, row_start=row_start)
+    xd = torch.from_numpy(xp).to(dev)
+    wd = torch.from_numpy(wp).to(dev)
+    yd = torch.empty((m, n_local), dtype=torch.int32, device=dev)
+
+    # For the microsecond-scale decode shape each timed launch gets its own copy of W so that
+    # it streams from HBM, not from L2.
+    rotate = bound == "hbm"
+    w_copies = [wd]
+    if rotate:
+        copies = max(2, int(2 * 126e6 // wp.nbytes) + 1)
+        w_copies = [wd] + [wd.clone() for _ in range(copies - 1)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step(i):
+        L.linear(xd, w_copies[i % len(w_copies)], out=yd)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    if L.last_status() != 0:
+        raise SystemExit("device-side failure during warm-up")
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.launch_count()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    if rotate:
+        # batch of launches between one event pair (a single 5 us launch is below event resolution)
+        flush.zero_()
+        starts[0].record()
+        for i in range(args.steps):
+            step(i)
+        ends[0].record()
+        barrier()
+        total_ms = starts[0].elapsed_time(ends[0])
+    else:
+        for i in range(args.steps):
+            flush.zero_()  # evict operands and result from L2 (test/benchmark.cu:93-96)
+            starts[i].record()
+            step(i)
+            ends[i].record()
+        barrier()
+        total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    launches = L.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if L.last_status() != 0:
+        raise SystemExit("device-side failure during the timed region")
+
+    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    ops = 2.0 * m * n_total * k
+    tops = ops / (ms_per_step * 1e-3) / 1e12
+    alg_bytes_local = m * k // 2 + n_local * k // 2 + 4 * m * n_local
+    gbs = alg_bytes_local * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- optional: all-gather of the Y shards (reported separately, never in `value`)
+    gather_ms = None
+    if args.gather and world > 1:
+        out = torch.empty((world, m, n_local), dtype=torch.int32, device=dev)
+        for _ in range(2):
+            dist.all_gather_into_tensor(out, yd)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            dist.all_gather_into_tensor(out, yd)
+        e1.record()
+        barrier()
+        g = torch.tensor([e0.elapsed_time(e1) / 5], dtype=torch.float64, device=dev)
+        dist.all_reduce(g, op=dist.ReduceOp.MAX)
+        gather_ms = float(g.item())
+
+    # ---- end to end through the host-buffer entry point
+    e2e = None
+    if not args.no_e2e:
+        xh = torch.from_numpy(xp).pin_memory()
+        wh = torch.from_numpy(wp).pin_memory()
+        yh = torch.empty((m, n_local), dtype=torch.int32).pin_memory()
+        xn, wn, yn = xh.numpy(), wh.numpy(), yh.numpy()
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            L.linear_host(xn, wn, k, out=yn)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            L.linear_host(xn, wn, k, out=yn)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item()) / e2e_steps
+        e2e = {"value": (ops / dt / 1e12) if bound == "tensor" else (alg_bytes_local * world / dt / 1e9),
+               "unit": "TOPS" if bound == "tensor" else "GB/s",
+               "h2d_bytes_per_step": int(xp.nbytes + wp.nbytes), "d2h_bytes_per_step": int(yn.nbytes),
+               "ms_per_step": dt * 1e3, "steps": e2e_steps,
+               "note": "X and W uploaded from pinned host memory and Y downloaded every step"}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    if bound == "tensor":
+        per_gpu = tops / world
+        peak = 2.0 * float(peaks["bf16_tflops"])
+        roofline = {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TOPS",
+                    "frac": per_gpu / peak,
+                    "peak_basis": f"2 x dense bf16 burst of {peak_kind} ({peaks['bf16_tflops']} TFLOP/s); "
+                                  "int8 issues at twice the bf16 rate on B200",
+                    "frac_of_nominal_int8_4500": per_gpu / NOMINAL_INT8_TOPS,
+                    "traffic": ncu_traffic(args.workload)}
+        value, unit = tops, "TOPS"
+    else:
+        per_gpu = gbs / world
+        peak = float(peaks["hbm_gbs"])
+        roofline = {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                    "peak_basis": f"{peak_kind} HBM copy bandwidth", "traffic": ncu_traffic(args.workload)}
+        value, unit = gbs, "GB/s"
+
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "s4 operands, s8 x s8 -> s32 tensor-core arithmetic",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: M={m} N={n_total} K={k}",
+                       "shard": f"{world} x (M={m}, N={n_local}, K={k}), W and Y split along N, X replicated",
+                       "l2": "256 MiB flush write before every timed launch" if not rotate
+                             else f"{len(w_copies)} rotating copies of W ({len(w_copies) * wp.nbytes >> 20} MiB > L2)",
+                       "kernel_path": {1: "tcgen05", 2: "legacy", 3: "skinny"}[L.path_for(m, n_local, k)]},
+            "tops": tops, "algorithmic_gbs": gbs,
+            "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline}
+    if e2e is not None:
+        line["e2e"] = e2e
+    if gather_ms is not None:
+        line["all_gather_ms"] = gather_ms
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_reference_sample(m, n_total, k)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
