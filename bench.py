@@ -257,11 +257,23 @@ def main():
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
     if rotate:
-        # batch of launches between one event pair (a single 5 us launch is below event resolution)
+        # A single ~5 us launch is below what an event pair (or a Python call) resolves, so the K
+        # steps are captured into one CUDA graph -- K launches, each on its own copy of W -- and
+        # the replay is timed as a whole.
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(args.steps):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(side)
+        launches0 = L.launch_count() - args.steps  # the capture issued the K launches
+        graph.replay()
+        barrier()
         flush.zero_()
         starts[0].record()
-        for i in range(args.steps):
-            step(i)
+        graph.replay()
         ends[0].record()
         barrier()
         total_ms = starts[0].elapsed_time(ends[0])

@@ -91,14 +91,21 @@ const char* int4_linear_status_string(int status);
 int int4_linear_set_path(int path);
 
 /* Tuning overrides for the tcgen05 family, for experiments and tests:
- * tile_n in {0 = automatic, 64, 128, 256} fixes the N extent of the output
- * tile; direct_store != 0 makes the epilogue write Y with per-thread vector
- * stores instead of shared-memory staging + TMA stores (always used when
- * n % 4 != 0).  Environment: INT4L_TILE_N, INT4L_EPILOGUE=direct. */
-int int4_linear_set_tuning(int tile_n, int direct_store);
+ * tile_n in {0 = automatic, 64, 128, 256} fixes the N extent of the
+ * single-CTA output tile; direct_store != 0 makes the epilogue write Y with
+ * per-thread vector stores instead of shared-memory staging + TMA stores
+ * (always used when n % 4 != 0); cta_pairs = 1 forces the 256 x 256 tile on a
+ * two-CTA cluster (cta_group::2), 0 forbids it, -1 leaves the choice to the
+ * dispatcher.  Environment: INT4L_TILE_N, INT4L_EPILOGUE=direct, INT4L_PAIRS. */
+int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
 
 /* Which family the dispatcher would use for a shape (INT4L_PATH_*). */
 int int4_linear_path_for(int m, int n, int k);
+
+/* Facts about the current device as this library sees them:
+ * what = 0 number of SMs, 1 number of two-CTA clusters of the GEMM kernel that
+ * can be resident at once.  Negative return = -status. */
+int int4_linear_device_info(int what);
 
 /* Number of kernels this library has launched in this process. */
 long long int4_linear_launch_count(void);

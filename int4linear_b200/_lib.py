@@ -16,8 +16,9 @@ SYMBOLS = {
     "int4_linear_last_status": (_I, []),
     "int4_linear_status_string": (ctypes.c_char_p, [_I]),
     "int4_linear_set_path": (_I, [_I]),
-    "int4_linear_set_tuning": (_I, [_I, _I]),
+    "int4_linear_set_tuning": (_I, [_I, _I, _I]),
     "int4_linear_path_for": (_I, [_I, _I, _I]),
+    "int4_linear_device_info": (_I, [_I]),
     "int4_linear_launch_count": (_LL, []),
     "int4_linear_version": (_I, []),
 }

@@ -34,20 +34,23 @@ def needs_build() -> bool:
     return any(os.path.getmtime(d) > t for d in _deps())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, out: str | None = None,
+          extra_flags: list[str] | None = None) -> str:
+    """Build the library.  `out` / `extra_flags` produce a variant (for example a
+    -DI4L_TRACE timeline build) next to the regular one without replacing it."""
+    if out is None and not force and not needs_build():
         return LIB
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found; cannot build libint4linear_b200.so")
     cmd = [nvcc, "-std=c++17", "-O3", "-shared", "-Xcompiler", "-fPIC",
            "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-           "-cudart", "static", "-o", LIB]
+           "-cudart", "static", "-o", out or LIB] + list(extra_flags or [])
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
     subprocess.run(cmd, check=True)
-    return LIB
+    return out or LIB
 
 
 if __name__ == "__main__":

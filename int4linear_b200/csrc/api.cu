@@ -21,6 +21,7 @@ std::atomic<long long> g_launches{0};
 std::atomic<int> g_path{-1};       // -1 = not yet read from the environment
 std::atomic<int> g_tile_n{0};      // 0 = automatic
 std::atomic<int> g_direct_store{-1};
+std::atomic<int> g_pairs{-2};      // -2 = not yet read from the environment
 thread_local int t_last_status = INT4L_OK;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -81,6 +82,17 @@ int forced_tile_n()
     if (v == 0) {
         const char* e = std::getenv("INT4L_TILE_N");
         if (e) v = std::atoi(e);
+    }
+    return v;
+}
+
+int forced_pairs()
+{
+    int v = g_pairs.load();
+    if (v == -2) {
+        const char* e = std::getenv("INT4L_PAIRS");
+        v = e ? (std::atoi(e) != 0 ? 1 : 0) : -1;
+        g_pairs.store(v);
     }
     return v;
 }
@@ -289,11 +301,13 @@ int int4_linear_set_path(int path)
     return prev;
 }
 
-int int4_linear_set_tuning(int tile_n, int direct_store)
+int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
 {
     if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return INT4L_ERR_INVALID_ARG;
+    if (cta_pairs < -1 || cta_pairs > 1) return INT4L_ERR_INVALID_ARG;
     g_tile_n.store(tile_n);
     g_direct_store.store(direct_store ? 1 : 0);
+    g_pairs.store(cta_pairs);
     return INT4L_OK;
 }
 
@@ -304,6 +318,16 @@ int int4_linear_path_for(int m, int n, int k)
     if (!ctx) return -rc;
     Problem p{nullptr, nullptr, nullptr, m, n, k};
     return choose_path(ctx, p);
+}
+
+int int4_linear_device_info(int what)
+{
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) return -rc;
+    if (what == 0) return ctx->sm_count;
+    if (what == 1) return ctx->max_pairs;
+    return -INT4L_ERR_INVALID_ARG;
 }
 
 long long int4_linear_launch_count(void) { return g_launches.load(); }

@@ -24,6 +24,7 @@ struct Problem {
 struct DeviceCtx {
     int device = -1;
     int sm_count = 0;
+    int max_pairs = 0;  // co-resident 2-CTA clusters of the GEMM kernel
     int cc_major = 0, cc_minor = 0;
     // Host-mapped word the kernels raise when a bounded wait expires.
     volatile int* status_host = nullptr;
@@ -68,5 +69,6 @@ bool skinny_supports(const DeviceCtx* ctx, const Problem& p);
 // Experiment knobs (int4_linear_set_tuning / INT4L_EPILOGUE, INT4L_TILE_N).
 bool getenv_flag_direct_store();
 int forced_tile_n();
+int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always
 
 }  // namespace i4l

@@ -6,15 +6,23 @@
 // (cp.async ring, XOR swizzle, ldmatrix, mma.sync m16n8k64, int2 stores).
 //
 // Work decomposition
-//   One persistent CTA per SM walks output tiles of 128 x BN.  K advances in
-//   blocks of 128 elements (64 packed bytes per row).
-//   Warp roles (448 threads):
+//   Persistent CTAs (one per SM) walk output tiles.  With CTAS == 1 a CTA owns a
+//   128 x BN tile.  With CTAS == 2 a cluster of two CTAs owns a 256 x BN tile and
+//   runs it as one cta_group::2 UMMA: each CTA loads and unpacks its own 128 rows
+//   of X and its own BN/2 rows of W (no multicast: every byte is fetched by the
+//   CTA that unpacks it), CTA 0 issues the instruction for the pair, and each
+//   CTA's tensor memory receives the accumulators of its own 128 rows.  Halving
+//   the W work per CTA matters because shared-memory bandwidth, not the tensor
+//   pipe, is what limits this kernel.  K advances in blocks of 128 elements
+//   (64 packed bytes per row).
+//   Warp roles (704 threads):
 //     warp 0      TMA producer: packed X tile (128 x 64 B) and W tile (BN x 64 B)
 //                 per K block into the "packed" ring; OOB rows/bytes read as 0,
 //                 which implements every M, N and K tail.
-//     warps 6-13  unpack: read the packed ring, expand nibbles to bytes, write
-//                 the "unpacked" ring in the UMMA K-major 128-byte-swizzled
-//                 layout, release the packed slot.
+//     warps 6-21  unpack, as two groups of eight warps that take alternate K
+//                 blocks: read the packed ring, expand nibbles to bytes, write the
+//                 "unpacked" ring in the UMMA K-major 128-byte-swizzled layout,
+//                 release the packed slot.
 //     warp 1      UMMA issuer: four 128 x BN x 32 tcgen05.mma per K block into one
 //                 of two TMEM accumulator buffers; tcgen05.commit releases the
 //                 unpacked slot / publishes the finished accumulator.
@@ -35,29 +43,54 @@
 #include "common.h"
 #include "ptx.cuh"
 
+// Optional timeline capture (compile with -DI4L_TRACE): the first worker records a clock
+// value at the hand-over points of each role for its first kTraceIters K blocks.  Off in
+// normal builds; exists to find where a pipeline stalls.
+#ifdef I4L_TRACE
+constexpr int kTraceIters = 192;
+__device__ long long i4l_trace_buf[2][5][kTraceIters][4];
+#define I4L_TRACE_PUT(role, it, slot)                                                         \
+    do {                                                                                      \
+        if (worker == 0 && (it) < kTraceIters) i4l_trace_buf[cta_rank][role][it][slot] = clock64(); \
+    } while (0)
+extern "C" int int4_linear_debug_trace(void* dst, int bytes)
+{
+    if (bytes > static_cast<int>(sizeof(i4l_trace_buf))) bytes = sizeof(i4l_trace_buf);
+    return cudaMemcpyFromSymbol(dst, i4l_trace_buf, bytes) == cudaSuccess ? bytes : -1;
+}
+#else
+#define I4L_TRACE_PUT(role, it, slot) do { } while (0)
+#endif
+
 namespace i4l {
 
 namespace {
 
 constexpr int kBM = 128;          // tile rows (UMMA M)
 constexpr int kBKBytes = 64;      // packed bytes per row per K block (128 elements)
-constexpr int kUnpackWarps = 8;
+constexpr int kGroups = 2;         // unpack groups, each converting every kGroups-th K block
+constexpr int kWarpsPerGroup = 8;
+constexpr int kUnpackWarps = kGroups * kWarpsPerGroup;
 constexpr int kThreads = 32 * (2 + 4 + kUnpackWarps);
 constexpr int kStoreStageBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
 
-template <int BN, int P, int U>
+template <int BN, int P, int U, int CTAS>
 struct Cfg {
     static constexpr int kBN = BN;
     static constexpr int kP = P;
     static constexpr int kU = U;
-    static constexpr int kPkStage = (kBM + BN) * kBKBytes;       // packed X then packed W
-    static constexpr int kUpStage = (kBM + BN) * 2 * kBKBytes;   // s8 X (16 KB) then s8 W
+    static constexpr int kCtas = CTAS;
+    static constexpr int kTileM = kBM * CTAS;                    // rows of the (cluster) tile
+    static constexpr int kRowsW = BN / CTAS;                     // W rows this CTA loads and unpacks
+    static constexpr int kPkStage = (kBM + kRowsW) * kBKBytes;     // packed X then packed W
+    static constexpr int kUpStage = (kBM + kRowsW) * 2 * kBKBytes; // s8 X (16 KB) then s8 W
     static constexpr int kTmemCols = 2 * BN;                     // two accumulator buffers
     static constexpr int kNumBarriers = 2 * P + 2 * U + 4;
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + U * kUpStage + P * kPkStage +
                                       kStoreStageBytes + kNumBarriers * 8 + 16;
-    static_assert(((kBM + BN) * 4) % (kUnpackWarps * 32) == 0, "unpack loop must divide evenly");
+    static_assert(P >= kGroups && U >= kGroups, "every unpack group needs a slot of its own");
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns: power of two");
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 template <class C, bool kTmaStore>
@@ -68,7 +101,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                        int* __restrict__ y, int m, int n, int k,
                        int tiles_m, int tiles_n, int* status)
 {
-    constexpr int BN = C::kBN, P = C::kP, U = C::kU;
+    constexpr int BN = C::kBN, P = C::kP, U = C::kU, CTAS = C::kCtas;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -91,11 +124,16 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    // Position in the pair (0 = the CTA that issues UMMA) and the id / count of work streams.
+    const uint32_t cta_rank = CTAS == 2 ? cluster_cta_rank() : 0u;
+    const int worker = CTAS == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
+    const int workers = CTAS == 2 ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
 
     if (tid == 0) {
-        for (int i = 0; i < P; ++i) { mbar_init(pk_full(i), 1); mbar_init(pk_empty(i), kUnpackWarps); }
-        for (int i = 0; i < U; ++i) { mbar_init(up_full(i), kUnpackWarps); mbar_init(up_empty(i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(tm_full(i), 1); mbar_init(tm_empty(i), 4); }
+        for (int i = 0; i < P; ++i) { mbar_init(pk_full(i), 1); mbar_init(pk_empty(i), kWarpsPerGroup); }
+        // up_full and tm_empty of CTA 0 collect the arrivals of both CTAs of a pair.
+        for (int i = 0; i < U; ++i) { mbar_init(up_full(i), kWarpsPerGroup * CTAS); mbar_init(up_empty(i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(tm_full(i), 1); mbar_init(tm_empty(i), 4 * CTAS); }
         *abort_flag = 0;
         mbar_init_fence();
         tma_prefetch_desc(&tm_x);
@@ -103,11 +141,11 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         if (kTmaStore) tma_prefetch_desc(&tm_y);
     }
     if (warp == 1) {
-        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
-        tmem_relinquish<1>();
+        tmem_alloc<CTAS>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+        tmem_relinquish<CTAS>();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -129,34 +167,39 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         if (lane == 0) {
             uint32_t it = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x) {
+            for (int tile = worker; alive && tile < num_tiles; tile += workers) {
                 int tm, tn;
                 tile_coord(tile, tm, tn);
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const uint32_t s = it % P, r = it / P;
+                    I4L_TRACE_PUT(0, it, 0);
                     if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                    I4L_TRACE_PUT(0, it, 1);
                     mbar_expect_tx(pk_full(s), C::kPkStage);
                     const uint32_t dst = pk_base + s * C::kPkStage;
-                    tma_load_2d(dst, &tm_x, pk_full(s), kb * kBKBytes, tm * kBM);
-                    tma_load_2d(dst + kBM * kBKBytes, &tm_w, pk_full(s), kb * kBKBytes, tn * BN);
+                    tma_load_2d(dst, &tm_x, pk_full(s), kb * kBKBytes, (tm * CTAS + cta_rank) * kBM);
+                    tma_load_2d(dst + kBM * kBKBytes, &tm_w, pk_full(s), kb * kBKBytes,
+                                tn * BN + cta_rank * C::kRowsW);
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------- UMMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_s8(kBM, BN);
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_s8(C::kTileM, BN);
             uint32_t it = 0, local_tile = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            for (int tile = worker; alive && tile < num_tiles; tile += workers, ++local_tile) {
                 const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
                 if (!mbar_wait(tm_empty(buf), (br & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const uint32_t s = it % U, r = it / U;
+                    I4L_TRACE_PUT(1, it, 0);
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
+                    I4L_TRACE_PUT(1, it, 1);
                     tc_fence_after_sync();
                     const uint32_t a_addr = up_base + s * C::kUpStage;
                     const uint64_t a_desc = umma_desc_sw128(a_addr);
@@ -164,11 +207,14 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // 32 bytes of K per instruction: advance the start address field by 32 >> 4.
-                        umma_i8<1>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
-                    umma_commit(up_empty(s));
+                    if constexpr (CTAS == 2) umma_commit_2cta(up_empty(s), 3); else umma_commit(up_empty(s));
+                    I4L_TRACE_PUT(1, it, 2);
                 }
-                if (alive) umma_commit(tm_full(buf));
+                if (alive) {
+                    if constexpr (CTAS == 2) umma_commit_2cta(tm_full(buf), 3); else umma_commit(tm_full(buf));
+                }
             }
         }
         __syncwarp();
@@ -180,13 +226,15 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         uint32_t local_tile = 0;
         uint32_t chunk_no = 0;
         bool alive = true;
-        for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+        for (int tile = worker; alive && tile < num_tiles; tile += workers, ++local_tile) {
             int tm, tn;
             tile_coord(tile, tm, tn);
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
+            if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 0);
             if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
+            if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 1);
             tc_fence_after_sync();
-            const int row0 = tm * kBM + sp * 32;
+            const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int row = row0 + lane;
             const int col0 = tn * BN;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
@@ -232,45 +280,69 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tm_empty(buf));
+            if (lane == 0) {
+                if constexpr (CTAS == 2) mbar_arrive_cluster(tm_empty(buf), 0); else mbar_arrive(tm_empty(buf));
+            }
+            if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 2);
         }
         if (kTmaStore && lane == 0) tma_store_wait_all<0>();
         __syncwarp();
     } else {
         // ------------------------------------------------------------ unpack
-        const int utid = tid - 6 * 32;  // 0 .. 255
-        constexpr int kChunks = (kBM + BN) * 4;  // 16-byte packed chunks per stage
+        // The unpack warps form kGroups independent groups; group g converts K blocks
+        // g, g + kGroups, ...  A block's conversion is a chain of latencies (wait, shared
+        // loads, shared stores, proxy fence, arrive), so several blocks must be in flight
+        // at once to keep the tensor pipe fed.
+        const int uw = warp - 6;
+        const int group = uw / kWarpsPerGroup;
+        const int gtid = (uw % kWarpsPerGroup) * 32 + lane;
+        constexpr int kGroupThreads = kWarpsPerGroup * 32;
+        constexpr int kChunks = (kBM + C::kRowsW) * 4;  // 16-byte packed chunks per stage
+        constexpr int kPerThread = kChunks / kGroupThreads;
+        static_assert(kChunks % kGroupThreads == 0, "unpack loop must divide evenly");
         uint32_t it = 0;
         bool alive = true;
-        for (int tile = blockIdx.x; alive && tile < num_tiles; tile += gridDim.x) {
+        for (int tile = worker; alive && tile < num_tiles; tile += workers) {
             for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
+                if (gtid == 0) I4L_TRACE_PUT(2, it, 0);
                 if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
-                if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                if (gtid == 0) I4L_TRACE_PUT(2, it, 1);
                 const uint32_t src = pk_base + ps * C::kPkStage;
                 const uint32_t dst = up_base + us * C::kUpStage;
+                // All loads first, so their latencies overlap.
+                uint4 x[kPerThread];
 #pragma unroll
-                for (int i = 0; i < kChunks / 256; ++i) {
-                    const int q = i * 256 + utid;
+                for (int i = 0; i < kPerThread; ++i) x[i] = lds128(src + (i * kGroupThreads + gtid) * 16);
+                if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                if (gtid == 0) I4L_TRACE_PUT(2, it, 2);
+#pragma unroll
+                for (int i = 0; i < kPerThread; ++i) {
+                    const int q = i * kGroupThreads + gtid;
                     const int r = q >> 2, c = q & 3;
-                    const uint4 x = lds128(src + q * 16);
                     uint4 lo, hi;
-                    lo.x = (x.x << 4) & 0xF0F0F0F0u; hi.x = x.x & 0xF0F0F0F0u;
-                    lo.y = (x.y << 4) & 0xF0F0F0F0u; hi.y = x.y & 0xF0F0F0F0u;
-                    lo.z = (x.z << 4) & 0xF0F0F0F0u; hi.z = x.z & 0xF0F0F0F0u;
-                    lo.w = (x.w << 4) & 0xF0F0F0F0u; hi.w = x.w & 0xF0F0F0F0u;
+                    lo.x = (x[i].x << 4) & 0xF0F0F0F0u; hi.x = x[i].x & 0xF0F0F0F0u;
+                    lo.y = (x[i].y << 4) & 0xF0F0F0F0u; hi.y = x[i].y & 0xF0F0F0F0u;
+                    lo.z = (x[i].z << 4) & 0xF0F0F0F0u; hi.z = x[i].z & 0xF0F0F0F0u;
+                    lo.w = (x[i].w << 4) & 0xF0F0F0F0u; hi.w = x[i].w & 0xF0F0F0F0u;
                     const uint32_t rowaddr = dst + r * 128;
                     const uint32_t sw = r & 7;
                     sts128(rowaddr + (((2 * c) ^ sw) << 4), lo);
                     sts128(rowaddr + (((2 * c + 1) ^ sw) << 4), hi);
                 }
+                if (gtid == 0) I4L_TRACE_PUT(4, it, 0);
                 fence_proxy_async_smem();
+                if (gtid == 0) I4L_TRACE_PUT(4, it, 1);
                 __syncwarp();
+                if (gtid == 0) I4L_TRACE_PUT(4, it, 2);
                 if (lane == 0) {
-                    mbar_arrive(up_full(us));
+                    if constexpr (CTAS == 2) mbar_arrive_cluster(up_full(us), 0); else mbar_arrive(up_full(us));
+                    if (gtid == 0) I4L_TRACE_PUT(4, it, 3);
                     mbar_arrive(pk_empty(ps));
                 }
+                if (gtid == 0) I4L_TRACE_PUT(2, it, 3);
             }
         }
     }
@@ -285,26 +357,30 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         for (int i = 0; i < 100; ++i) __nanosleep(1000);
         __syncthreads();
     }
+    // A pair frees its tensor memory together, and neither CTA may leave while the
+    // other can still signal its barriers.
+    if constexpr (CTAS == 2) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, C::kTmemCols);
+        tmem_dealloc<CTAS>(tmem_base, C::kTmemCols);
     }
 }
 
-using Cfg256 = Cfg<256, 3, 2>;
-using Cfg128 = Cfg<128, 4, 3>;
-using Cfg64 = Cfg<64, 4, 4>;
+using Cfg256 = Cfg<256, 3, 2, 1>;
+using Cfg128 = Cfg<128, 4, 3, 1>;
+using Cfg64 = Cfg<64, 4, 4, 1>;
+using Cfg256x2 = Cfg<256, 4, 3, 2>;  // 256 x 256 tile on a CTA pair
 
 template <class C, bool kTmaStore>
 int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
-    const int tiles_m = (p.m + kBM - 1) / kBM;
+    const int tiles_m = (p.m + C::kTileM - 1) / C::kTileM;
     const int tiles_n = (p.n + C::kBN - 1) / C::kBN;
     const uint64_t pitch = static_cast<uint64_t>(p.k) / 2;
     CUtensorMap tm_x, tm_w, tm_y;
     int rc = make_tensor_map_2d(ctx, &tm_x, p.x, 1, pitch, p.m, pitch, kBKBytes, kBM, false);
     if (rc != INT4L_OK) return rc;
-    rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kBN, false);
+    rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW, false);
     if (rc != INT4L_OK) return rc;
     if (kTmaStore) {
         rc = make_tensor_map_2d(ctx, &tm_y, p.y, 4, p.n, p.m, static_cast<uint64_t>(p.n) * 4, 32, 32, true);
@@ -312,11 +388,25 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     } else {
         tm_y = tm_x;  // unused by the kernel
     }
-    const int grid = min(tiles_m * tiles_n, ctx->sm_count);
-    gemm_s4_tcgen05_kernel<C, kTmaStore><<<grid, kThreads, C::kSmemBytes, stream>>>(
-        tm_x, tm_w, tm_y, static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, ctx->status_dev);
+    const int max_workers = C::kCtas == 2 ? ctx->max_pairs : ctx->sm_count;
+    const int workers = min(tiles_m * tiles_n, max_workers);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(workers * C::kCtas, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = C::kCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_kernel<C, kTmaStore>, tm_x, tm_w, tm_y,
+                                       static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, ctx->status_dev);
     count_launch();
-    return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+    if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+    return INT4L_OK;
 }
 
 template <class C>
@@ -332,12 +422,33 @@ int set_attr()
 
 }  // namespace
 
-int setup_tcgen05(DeviceCtx*)
+int setup_tcgen05(DeviceCtx* ctx)
 {
     int rc = set_attr<Cfg256>();
     if (rc == INT4L_OK) rc = set_attr<Cfg128>();
     if (rc == INT4L_OK) rc = set_attr<Cfg64>();
-    return rc;
+    if (rc == INT4L_OK) rc = set_attr<Cfg256x2>();
+    if (rc != INT4L_OK) return rc;
+    // How many CTA pairs the device can hold at once (pairs must sit in one GPC-level
+    // neighbourhood, so this can be below sm_count / 2).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * ctx->sm_count, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg256x2::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int pairs = 0;
+    if (cudaOccupancyMaxActiveClusters(&pairs, gemm_s4_tcgen05_kernel<Cfg256x2, true>, &cfg) != cudaSuccess || pairs <= 0) {
+        cudaGetLastError();
+        pairs = ctx->sm_count / 2;
+    }
+    ctx->max_pairs = pairs < ctx->sm_count / 2 ? pairs : ctx->sm_count / 2;
+    return INT4L_OK;
 }
 
 // Tile-width choice: the widest N tile that still yields at least one tile per
@@ -353,6 +464,13 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     if (bn == 128 && tiles(128) < ctx->sm_count) bn = 64;
     const int forced = forced_tile_n();
     if (forced == 64 || forced == 128 || forced == 256) bn = forced;
+    // CTA pairs once there are at least as many 256 x 256 tiles as pairs (and more than one
+    // row block, or the second CTA of each pair would multiply zeros).
+    const long long pair_tiles = ((p.m + 255) / 256) * static_cast<long long>((p.n + 255) / 256);
+    bool pairs = p.m > 128 && pair_tiles >= ctx->max_pairs;
+    if (forced != 0) pairs = false;
+    if (forced_pairs() >= 0) pairs = forced_pairs() != 0;
+    if (pairs) return tma_store ? launch_cfg<Cfg256x2, true>(ctx, p, stream) : launch_cfg<Cfg256x2, false>(ctx, p, stream);
     if (bn == 256) return tma_store ? launch_cfg<Cfg256, true>(ctx, p, stream) : launch_cfg<Cfg256, false>(ctx, p, stream);
     if (bn == 128) return tma_store ? launch_cfg<Cfg128, true>(ctx, p, stream) : launch_cfg<Cfg128, false>(ctx, p, stream);
     return tma_store ? launch_cfg<Cfg64, true>(ctx, p, stream) : launch_cfg<Cfg64, false>(ctx, p, stream);

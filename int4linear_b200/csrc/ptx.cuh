@@ -36,6 +36,30 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ----------------------------------------------------------------- cluster --
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_count_x() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// Full barrier over every thread of the cluster (hardware barrier; all threads
+// always reach it because every software wait before it is bounded).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier --
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -54,12 +78,16 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // Arrive on the barrier at the same shared-memory offset in CTA `cta` of this cluster.
+// Release semantics at CTA scope (the default), as for a local arrive: the data the
+// arrival publishes was written to shared memory through the generic proxy and fenced
+// towards the async proxy by its writers, which is all the consumer (UMMA) needs.  A
+// cluster-scope release here costs over a thousand cycles per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) {
     asm volatile(
         "{\n\t"
         ".reg .b32 remote;\n\t"
         "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
-        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t"
         "}\n" ::"r"(bar), "r"(cta)
         : "memory");
 }

@@ -139,8 +139,8 @@ def set_path(path: int) -> int:
     return _lib.load().int4_linear_set_path(path)
 
 
-def set_tuning(tile_n: int = 0, direct_store: bool = False) -> None:
-    st = _lib.load().int4_linear_set_tuning(tile_n, 1 if direct_store else 0)
+def set_tuning(tile_n: int = 0, direct_store: bool = False, cta_pairs: int = -1) -> None:
+    st = _lib.load().int4_linear_set_tuning(tile_n, 1 if direct_store else 0, cta_pairs)
     if st != 0:
         raise Int4LinearError(st, "int4_linear_set_tuning")
 

@@ -9,7 +9,7 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False):
+def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False, pairs=-1):
     """Upload packed operands, run one blocking launch through the C ABI, download Y."""
     import torch
     xd = torch.from_numpy(xp).to(cuda)
@@ -17,12 +17,12 @@ def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False):
     m, n = xp.shape[0], wp.shape[0]
     yd = torch.full((m, n), -12345, dtype=torch.int32, device=cuda)
     prev = L.set_path(path)
-    L.set_tuning(tile_n, direct)
+    L.set_tuning(tile_n, direct, pairs)
     try:
         L.linear_v21_launch(xd, wd, yd, m, n, k)
     finally:
         L.set_path(prev)
-        L.set_tuning(0, False)
+        L.set_tuning(0, False, -1)
     return yd.cpu().numpy()
 
 
@@ -31,6 +31,8 @@ VARIANTS = [
     ("tcgen05-256-direct", dict(path=L.PATH_TCGEN05, tile_n=256, direct=True)),
     ("tcgen05-128-tma", dict(path=L.PATH_TCGEN05, tile_n=128, direct=False)),
     ("tcgen05-64-direct", dict(path=L.PATH_TCGEN05, tile_n=64, direct=True)),
+    ("tcgen05-pairs-tma", dict(path=L.PATH_TCGEN05, pairs=1)),
+    ("tcgen05-pairs-direct", dict(path=L.PATH_TCGEN05, pairs=1, direct=True)),
     ("legacy", dict(path=L.PATH_LEGACY)),
     ("auto", dict(path=L.PATH_AUTO)),
 ]

@@ -70,8 +70,9 @@ def test_argument_checks_need_no_gpu():
     assert lib.int4_linear_launch_async(*ok, 8, 8, 131072, None) == 2  # k too large
     assert lib.int4_linear_launch_async(base + 4, base, base, 8, 8, 32, None) == 3
     assert lib.int4_linear_status_string(2).decode().startswith("unsupported")
-    assert lib.int4_linear_set_tuning(100, 0) == 1
-    assert lib.int4_linear_set_tuning(0, 0) == 0
+    assert lib.int4_linear_set_tuning(100, 0, -1) == 1
+    assert lib.int4_linear_set_tuning(0, 0, 2) == 1
+    assert lib.int4_linear_set_tuning(0, 0, -1) == 0
 
 
 def test_no_gpu_means_error_not_fallback():
