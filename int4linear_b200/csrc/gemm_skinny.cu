@@ -23,6 +23,8 @@
 //
 // Replaces, for these shapes, the reference's kernels/linear_v21.h:471-753
 // (which runs them as 256 x 128 tiles that are almost entirely padding).
+#include <cstdlib>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -158,10 +160,256 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
     }
 }
 
+
+// Register-resident variant for m <= 16 and K <= 8192 (the decode shape proper).
+// Each of the 16 warps owns a fixed slice of K (KBW blocks of 128 elements) for every
+// W group of the CTA, so its X fragments are loaded and expanded ONCE into registers and
+// the inner loop is nothing but: one 16-byte streaming load per lane and K block, eight
+// ALU operations to expand it, four MMAs.  Weight loads for several groups ahead are kept
+// in flight, and the first of them are issued before anything else happens in the kernel,
+// so HBM is busy from the first cycle; X never goes through shared memory.
+template <int KBW>
+__global__ void __launch_bounds__(kSkinnyThreads, 1)
+gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
+                          int m, int n, int k, int groups_total)
+{
+    constexpr int D = 8 / KBW;  // groups of loads in flight per warp
+    extern __shared__ __align__(16) uint8_t smem[];
+    int* acc = reinterpret_cast<int*>(smem);  // [groups][16][8]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int row_bytes = k >> 1;
+    const int g_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * groups_total / gridDim.x);
+    const int g_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * groups_total / gridDim.x);
+    const int n_groups = g_end - g_begin;
+
+    // Byte offset of this lane's 16 bytes inside a row, per K block of the warp's slice.
+    const int col0 = warp * KBW * 64 + q * 16;
+    bool col_ok[KBW];
+#pragma unroll
+    for (int u = 0; u < KBW; ++u) col_ok[u] = col0 + u * 64 < row_bytes;
+
+    auto load_group = [&](int gi, uint4 (&dst)[KBW]) {
+        const int wrow = (g_begin + gi) * 8 + g;
+        const bool ok = gi < n_groups && wrow < n;
+        const uint8_t* p = w + static_cast<size_t>(ok ? wrow : 0) * row_bytes + col0;
+#pragma unroll
+        for (int u = 0; u < KBW; ++u)
+            dst[u] = (ok && col_ok[u]) ? ldg_stream(p + u * 64) : make_uint4(0, 0, 0, 0);
+    };
+
+    uint4 wv[D][KBW];
+#pragma unroll
+    for (int d = 0; d < D; ++d) load_group(d, wv[d]);
+
+    // X fragments of this warp's K slice: rows g and g + 8, expanded to bytes.
+    uint32_t a[KBW][4][4];
+#pragma unroll
+    for (int u = 0; u < KBW; ++u) {
+        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+        if (col_ok[u]) {
+            if (g < m) x0 = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(g) * row_bytes + col0 + u * 64);
+            if (g + 8 < m) x1 = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(g + 8) * row_bytes + col0 + u * 64);
+        }
+        const uint32_t r0[4] = {x0.x, x0.y, x0.z, x0.w};
+        const uint32_t r1[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            a[u][e][0] = (r0[e] << 4) & 0xF0F0F0F0u;
+            a[u][e][1] = (r1[e] << 4) & 0xF0F0F0F0u;
+            a[u][e][2] = r0[e] & 0xF0F0F0F0u;
+            a[u][e][3] = r1[e] & 0xF0F0F0F0u;
+        }
+    }
+
+    for (int i = tid; i < n_groups * 128; i += kSkinnyThreads) acc[i] = 0;
+    __syncthreads();
+
+    for (int gi0 = 0; gi0 < n_groups; gi0 += D) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            const int gi = gi0 + d;
+            if (gi < n_groups) {
+                int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int u = 0; u < KBW; ++u) {
+                    const uint32_t ww[4] = {wv[d][u].x, wv[d][u].y, wv[d][u].z, wv[d][u].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        mma_s8(c, a[u][e][0], a[u][e][1], a[u][e][2], a[u][e][3],
+                               (ww[e] << 4) & 0xF0F0F0F0u, ww[e] & 0xF0F0F0F0u);
+                }
+                load_group(gi + D, wv[d]);
+                int* o = acc + gi * 128;
+                atomicAdd(o + g * 8 + 2 * q, c[0] >> 8);
+                atomicAdd(o + g * 8 + 2 * q + 1, c[1] >> 8);
+                atomicAdd(o + (g + 8) * 8 + 2 * q, c[2] >> 8);
+                atomicAdd(o + (g + 8) * 8 + 2 * q + 1, c[3] >> 8);
+            }
+        }
+    }
+    __syncthreads();
+
+    const int cols = n_groups * 8;
+    const int col_base = g_begin * 8;
+    for (int i = tid; i < m * cols; i += kSkinnyThreads) {
+        const int r = i / cols, cc = i - r * cols;
+        const int col = col_base + cc;
+        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)];
+    }
+}
+
+
+// TMA variant for m <= 16: the decode shape proper.
+// Every warp owns K slices of 128 packed bytes (256 elements).  For a slice it asks TMA
+// for a box of [R rows x 128 B] of W -- all rows of the CTA's run at once when they fit,
+// so that the whole weight slab of the CTA is requested in the first microsecond of the
+// kernel and HBM can stream without waiting for anybody's registers -- into a private,
+// 128-byte-swizzled buffer, and then walks the rows eight at a time with ldmatrix, which
+// hands lane (g, q) four bytes of row g for each of four 16-byte chunks: exactly one
+// m16n8k32 B fragment per register after the nibble expansion.  X fragments (the same
+// bytes of rows g and g + 8 of X) stay in registers for the slice.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(kSkinnyThreads, 1)
+gemm_s4_skinny_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const uint8_t* __restrict__ x,
+                          int* __restrict__ y, int m, int n, int k, int groups_total,
+                          int stage_rows, int n_buffers, int* status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - raw);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int row_bytes = k >> 1;
+    const int n_slices = (row_bytes + 127) >> 7;
+    const int g_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * groups_total / gridDim.x);
+    const int g_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * groups_total / gridDim.x);
+    const int n_groups = g_end - g_begin;
+    const int stage_groups = stage_rows >> 3;
+    const int passes = (n_groups + stage_groups - 1) / stage_groups;
+
+    // Layout: [16 warps][n_buffers][stage_rows x 128 B] | barriers [16][4] | abort | acc
+    const uint32_t stage_bytes = static_cast<uint32_t>(stage_rows) * 128u;
+    const uint32_t buf0 = base + (warp * n_buffers) * stage_bytes;
+    const uint32_t bar_off = 16u * n_buffers * stage_bytes;
+    const uint32_t bar0 = base + bar_off + warp * 32u;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + bar_off + 16 * 32);
+    int* acc = reinterpret_cast<int*>(gbase + bar_off + 16 * 32 + 16);  // [groups][16][8]
+
+    // Items of this warp in consumption order: slice-major over its slices, row passes inside.
+    const int my_slices = warp < n_slices ? (n_slices - warp + 15) / 16 : 0;
+    const int n_items = my_slices * passes;
+    auto issue = [&](int item) {
+        const int s = warp + 16 * (item / passes), p = item % passes;
+        const int b = item % n_buffers;
+        mbar_expect_tx(bar0 + 8u * b, stage_bytes);
+        tma_load_2d(buf0 + b * stage_bytes, &tm_w, bar0 + 8u * b, s * 128, (g_begin + p * stage_groups) * 8);
+    };
+
+    if (tid == 0) *abort_flag = 0;
+    if (lane == 0) {
+        for (int b = 0; b < n_buffers; ++b) mbar_init(bar0 + 8u * b, 1);
+        mbar_init_fence();
+        for (int it = 0; it < n_items && it < n_buffers; ++it) issue(it);
+    }
+    for (int i = tid; i < n_groups * 128; i += kSkinnyThreads) acc[i] = 0;
+    __syncthreads();
+
+    uint32_t a[2][4][4];  // [half of the slice][16-byte chunk][a0..a3]
+    int cur_slice = -1;
+    bool alive = true;
+    for (int item = 0; alive && item < n_items; ++item) {
+        const int s = warp + 16 * (item / passes), p = item % passes;
+        const int b = item % n_buffers;
+        if (s != cur_slice) {
+            cur_slice = s;
+            // X words for this slice: byte offset of chunk j in half h is s*128 + h*64 + 16j + 4q.
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int off = s * 128 + h * 64 + j * 16 + q * 4;
+                    uint32_t r0 = 0, r1 = 0;
+                    if (off < row_bytes) {
+                        if (g < m) r0 = __ldg(reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(g) * row_bytes + off));
+                        if (g + 8 < m) r1 = __ldg(reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(g + 8) * row_bytes + off));
+                    }
+                    a[h][j][0] = (r0 << 4) & 0xF0F0F0F0u;
+                    a[h][j][1] = (r1 << 4) & 0xF0F0F0F0u;
+                    a[h][j][2] = r0 & 0xF0F0F0F0u;
+                    a[h][j][3] = r1 & 0xF0F0F0F0u;
+                }
+        }
+        if (!mbar_wait(bar0 + 8u * b, (item / n_buffers) & 1u, abort_flag)) { alive = false; break; }
+        const uint32_t buf = buf0 + b * stage_bytes;
+        const int groups_here = min(stage_groups, n_groups - p * stage_groups);
+        // ldmatrix row address of this lane: row (lane & 7) of the group, chunk (lane >> 3).
+        const uint32_t lrow = lane & 7, lchunk = lane >> 3;
+        for (int gi = 0; gi < groups_here; ++gi) {
+            const uint32_t rowaddr = buf + (gi * 8 + lrow) * 128u;
+            uint32_t w0[4], w1[4];
+            ldmatrix_x4(rowaddr + ((lchunk ^ lrow) << 4), w0);
+            ldmatrix_x4(rowaddr + (((4 + lchunk) ^ lrow) << 4), w1);
+            int c[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                mma_s8(c, a[0][j][0], a[0][j][1], a[0][j][2], a[0][j][3], (w0[j] << 4) & 0xF0F0F0F0u, w0[j] & 0xF0F0F0F0u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                mma_s8(c, a[1][j][0], a[1][j][1], a[1][j][2], a[1][j][3], (w1[j] << 4) & 0xF0F0F0F0u, w1[j] & 0xF0F0F0F0u);
+            int* o = acc + (p * stage_groups + gi) * 128;
+            atomicAdd(o + g * 8 + 2 * q, c[0] >> 8);
+            atomicAdd(o + g * 8 + 2 * q + 1, c[1] >> 8);
+            atomicAdd(o + (g + 8) * 8 + 2 * q, c[2] >> 8);
+            atomicAdd(o + (g + 8) * 8 + 2 * q + 1, c[3] >> 8);
+        }
+        // Refill this buffer with the item that will use it next.
+        if (item + n_buffers < n_items) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) issue(item + n_buffers);
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0) atomicExch(status, INT4L_ERR_DEVICE_TIMEOUT);
+        for (int i = 0; i < 100; ++i) __nanosleep(1000);
+        return;
+    }
+
+    const int cols = n_groups * 8;
+    const int col_base = g_begin * 8;
+    for (int i = tid; i < m * cols; i += kSkinnyThreads) {
+        const int r = i / cols, cc = i - r * cols;
+        const int col = col_base + cc;
+        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)];
+    }
+}
+
 struct SkinnyPlan {
     int mb, grid, groups_total, groups_per_cta_max, x_pitch;
     size_t smem;
 };
+
+// Experiment knob INT4L_SKINNY: 0 automatic (register variant, else TMA variant, else the
+// shared-memory variant), 1 never the TMA variant, 2 shared-memory variant only, 3 never the
+// register variant.
+int skinny_variant()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("INT4L_SKINNY");
+        v = e ? atoi(e) : 0;
+    }
+    return v;
+}
 
 bool plan_skinny(const DeviceCtx* ctx, const Problem& p, SkinnyPlan* out)
 {
@@ -195,6 +443,10 @@ int setup_skinny(DeviceCtx*)
     cudaError_t e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     return e == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }
 
@@ -205,6 +457,46 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     const uint8_t* x = static_cast<const uint8_t*>(p.x);
     const uint8_t* w = static_cast<const uint8_t*>(p.w);
     int* y = static_cast<int*>(p.y);
+    const int kb_count = (p.k + 127) / 128;
+    if (p.m <= 16 && kb_count >= 16 && kb_count <= 64 && skinny_variant() != 2 && skinny_variant() != 3) {
+        const size_t smem = static_cast<size_t>(s.groups_per_cta_max) * 128 * sizeof(int);
+        if (kb_count <= 16)
+            gemm_s4_skinny_reg_kernel<1><<<s.grid, kSkinnyThreads, smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total);
+        else if (kb_count <= 32)
+            gemm_s4_skinny_reg_kernel<2><<<s.grid, kSkinnyThreads, smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total);
+        else
+            gemm_s4_skinny_reg_kernel<4><<<s.grid, kSkinnyThreads, smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total);
+        count_launch();
+        return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+    }
+    if (p.m <= 16 && p.k >= 256 && skinny_variant() != 2) {
+        // Whole slab resident when it fits (one buffer per warp holding every row of the CTA's
+        // run for the warp's slice), otherwise two 48-row buffers per warp.
+        const int rows_max = s.groups_per_cta_max * 8;
+        const int n_slices = (p.k / 2 + 127) / 128;
+        const size_t fixed = 1024 + 16 * 32 + 16 + static_cast<size_t>(s.groups_per_cta_max) * 128 * sizeof(int);
+        int stage_rows = rows_max, n_buffers = 1;
+        if (rows_max > 256 || n_slices > 16 || fixed + 16ull * rows_max * 128 > 227 * 1024) {
+            stage_rows = 48;
+            n_buffers = 2;
+        }
+        if (const char* e = getenv("INT4L_SKINNY_ROWS")) {  // experiment: explicit stage geometry
+            stage_rows = atoi(e);
+            const char* b = getenv("INT4L_SKINNY_BUFS");
+            n_buffers = b ? atoi(b) : 2;
+        }
+        const size_t smem = fixed + 16ull * n_buffers * stage_rows * 128;
+        if (smem <= 227 * 1024 && skinny_variant() != 1) {
+            CUtensorMap tm_w;
+            const uint64_t pitch = static_cast<uint64_t>(p.k) / 2;
+            int rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, 128, stage_rows, true);
+            if (rc != INT4L_OK) return rc;
+            gemm_s4_skinny_tma_kernel<<<s.grid, kSkinnyThreads, smem, stream>>>(
+                tm_w, x, y, p.m, p.n, p.k, s.groups_total, stage_rows, n_buffers, ctx->status_dev);
+            count_launch();
+            return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+        }
+    }
     if (s.mb == 1)
         gemm_s4_skinny_kernel<1><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch);
     else if (s.mb == 2)
