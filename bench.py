@@ -168,13 +168,49 @@ def cpu_reference_sample(m, n, k, seconds_target=15.0):
             "sample": f"rows 0..{rows - 1} of M={m} (N={n}, K={k}), {rows // cores} rows per thread, {dt:.1f} s"}
 
 
+def reference_gpu_arm(args, m, n, k):
+    import torch
+    from int4linear_b200 import uniform_s4_packed
+    from oracle import oracle as O
+    ref = O.ref_lib()
+    if ref is None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref was not built (needs the reference checkout)"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    xd = torch.from_numpy(uniform_s4_packed(0xA008, m, k)).to(dev)
+    wd = torch.from_numpy(uniform_s4_packed(0xB008, n, k)).to(dev)
+    yd = torch.empty((m, n), dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(3, args.warmup)):
+        ref.ref_linear_v21_launch(xd.data_ptr(), wd.data_ptr(), yd.data_ptr(), m, n, k)
+    times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ref.ref_linear_v21_launch(xd.data_ptr(), wd.data_ptr(), yd.data_ptr(), m, n, k)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = sum(times) / len(times)
+    tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    print(json.dumps({"impl": "reference-gpu", "metric": f"INT4 GEMM TOPS at M={m} N={n} K={k}", "value": tops,
+                      "unit": "TOPS", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+                      "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": f"{args.workload}: M={m} N={n} K={k}",
+                                 "kernel": "reference linear_v21 (mma.sync m16n8k64 s4) built for sm_100a"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="m8", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
+    ap.add_argument("--path", default="auto", choices=["auto", "tcgen05", "legacy", "skinny"],
+                    help="force one kernel family of this library (default: shape dispatch)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -202,10 +238,21 @@ def main():
         print(json.dumps(line))
         return
 
+    if args.impl == "reference-gpu":
+        # The north star's path (b): the reference's own kernel (cp.async + ldmatrix + mma.sync
+        # m16n8k64 s4, kernels/linear_v21.h) recompiled for sm_100a from its unmodified sources
+        # into oracle/_ref, timed with the same method.  A comparison arm, not this library.
+        if rank != 0:
+            return
+        reference_gpu_arm(args, m, n_work, k)
+        return
+
     import torch
     import torch.distributed as dist
     import int4linear_b200 as L
 
+    L.set_path({"auto": L.PATH_AUTO, "tcgen05": L.PATH_TCGEN05, "legacy": L.PATH_LEGACY,
+                "skinny": L.PATH_SKINNY}[args.path])
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -374,7 +421,8 @@ def main():
                        "shard": f"{world} x (M={m}, N={n_local}, K={k}), W and Y split along N, X replicated",
                        "l2": "256 MiB flush write before every timed launch" if not rotate
                              else f"{len(w_copies)} rotating copies of W ({len(w_copies) * wp.nbytes >> 20} MiB > L2)",
-                       "kernel_path": {1: "tcgen05", 2: "legacy", 3: "skinny"}[L.path_for(m, n_local, k)]},
+                       "kernel_path": args.path if args.path != "auto"
+                       else {1: "tcgen05", 2: "legacy", 3: "skinny"}[L.path_for(m, n_local, k)]},
             "tops": tops, "algorithmic_gbs": gbs,
             "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline}
     if e2e is not None:

@@ -53,5 +53,21 @@ def build(force: bool = False, verbose: bool = False, out: str | None = None,
     return out or LIB
 
 
+def build_compat_check() -> str:
+    """Compile tests/compat_check.cu against the drop-in header and the library."""
+    root = os.path.dirname(PKG)
+    src = os.path.join(root, "tests", "compat_check.cu")
+    out = os.path.join(root, "tests", "compat_check.bin")
+    hdr = os.path.join(PKG, "compat", "kernels", "linear_v21.h")
+    if os.path.exists(out) and os.path.getmtime(out) >= max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(build())):
+        return out
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = [nvcc, "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+           "-I", os.path.join(PKG, "compat"), src, "-L", PKG, "-lint4linear_b200",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../int4linear_b200", "-o", out]
+    subprocess.run(cmd, check=True)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,110 @@
+"""N-sharding of the linear layer across the GPUs of one node.
+
+Y[:, j0:j1] = X @ W[j0:j1, :]^T, and W is stored N x K row-major, so an N-shard of W
+is one contiguous byte range.  Every rank keeps the full X (replicated into its own
+HBM) and its own rows of W, runs the single-GPU operator on (M, N/g, K) and owns the
+matching columns of Y.  The GEMM needs no exchange at all; the only collective is the
+OPTIONAL all-gather of Y for callers that want the full result everywhere.  The
+reference has no multi-GPU code, so this module has no counterpart there; the
+single-GPU operator it drives is the launcher of kernels/linear_v21.cu:9-49.
+
+One process per GPU; `torch.distributed` (NCCL on GPUs, gloo in CPU tests) is the
+plumbing.  Nothing here computes the operator on the CPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class Shard:
+    rank: int
+    world: int
+    row_start: int  # first row of W (= first column of Y) this rank owns
+    rows: int       # number of rows of W (= columns of Y)
+
+
+def shard_bounds(n: int, world: int, rank: int, align: int = 256) -> Shard:
+    """Contiguous, balanced split of N in units of `align` rows (the widest output tile),
+    so that no rank gets a ragged tile unless N itself is ragged.  Earlier ranks take the
+    remainder units; the last non-empty rank absorbs the tail of N."""
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    if n <= 0:
+        raise ValueError("n must be positive")
+    units = (n + align - 1) // align
+    base, extra = divmod(units, world)
+    u0 = rank * base + min(rank, extra)
+    u1 = u0 + base + (1 if rank < extra else 0)
+    r0, r1 = min(u0 * align, n), min(u1 * align, n)
+    return Shard(rank, world, r0, r1 - r0)
+
+
+def all_shards(n: int, world: int, align: int = 256) -> list[Shard]:
+    return [shard_bounds(n, world, r, align) for r in range(world)]
+
+
+def shard_rows(w_packed, shard: Shard):
+    """The rows of a full packed W (tensor or ndarray, [N, K/2]) that `shard` owns -- a view."""
+    return w_packed[shard.row_start:shard.row_start + shard.rows]
+
+
+def forward_local(x_packed, w_shard_packed, k: int | None = None, out=None):
+    """This rank's columns of Y: the single-GPU operator on its shard (asynchronous)."""
+    from .linear import linear
+    return linear(x_packed, w_shard_packed, k=k, out=out)
+
+
+def gather_columns(y_local, n: int, group=None, align: int = 256):
+    """All-gather of the column shards into the full [M, N] result on every rank.
+
+    A row-major Y split by columns is not a contiguous concatenation, so the shards are
+    gathered as [world][M][n_r] blocks and then copied into place.  Handles uneven shards
+    (ranks may own different column counts, including zero)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    shards = all_shards(n, world, align)
+    m = y_local.shape[0]
+    rank = dist.get_rank(group)
+    if y_local.shape[1] != shards[rank].rows:
+        raise ValueError("local result does not match this rank's shard")
+    full = torch.empty((m, n), dtype=y_local.dtype, device=y_local.device)
+    if all(s.rows == shards[0].rows for s in shards):
+        stacked = torch.empty((world * m, shards[0].rows), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(stacked, y_local.contiguous(), group=group)
+        full.view(m, world, shards[0].rows).copy_(stacked.view(world, m, shards[0].rows).permute(1, 0, 2))
+    else:
+        # pad every shard to the widest one so a single collective moves everything
+        widest = max(s.rows for s in shards)
+        mine = torch.zeros((m, widest), dtype=y_local.dtype, device=y_local.device)
+        mine[:, :y_local.shape[1]] = y_local
+        stacked = torch.empty((world * m, widest), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(stacked, mine, group=group)
+        stacked = stacked.view(world, m, widest)
+        for s in shards:
+            if s.rows:
+                full[:, s.row_start:s.row_start + s.rows] = stacked[s.rank, :, :s.rows]
+    return full
+
+
+class ShardedInt4Linear:
+    """A weight-stationary N-sharded layer: holds this rank's rows of W on its GPU."""
+
+    def __init__(self, w_shard_packed, n_total: int, k: int, group=None, align: int = 256):
+        import torch.distributed as dist
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.shard = shard_bounds(n_total, self.world, self.rank, align)
+        if w_shard_packed.shape[0] != self.shard.rows:
+            raise ValueError("weight shard has the wrong number of rows for this rank")
+        self.w = w_shard_packed
+        self.n_total, self.k, self.align = n_total, k, align
+
+    def forward(self, x_packed, gather: bool = False):
+        y = forward_local(x_packed, self.w, self.k)
+        if gather and self.world > 1:
+            return gather_columns(y, self.n_total, self.group, self.align)
+        return y

@@ -68,7 +68,42 @@ def build_ref(force: bool = False) -> str | None:
     return out
 
 
+def build_dropin(force: bool = False) -> list[str]:
+    """Drop-in check: the reference's OWN harness sources, unchanged and compiled where they
+    lie, against this repository's replacement header and library.
+        oracle/_ref/test_correctness_dropin   test/test_correctness.cu + utils/packer.cpp,
+                                              linear_v21_launch resolved from the library
+        oracle/_ref/benchmark_dropin          test/benchmark.cu + utils/packer.cpp, kernel
+                                              template taken from the compat header
+    Only possible where the reference checkout exists; returns the files built."""
+    if not reference_available():
+        return []
+    repo = os.path.dirname(HERE)
+    pkg = os.path.join(repo, "int4linear_b200")
+    lib = os.path.join(pkg, "libint4linear_b200.so")
+    if not os.path.exists(lib):
+        return []
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    out_dir = os.path.join(HERE, "_ref")
+    os.makedirs(out_dir, exist_ok=True)
+    built = []
+    common = [nvcc, "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+              "-I", os.path.join(pkg, "compat"), "-I", REFERENCE_ROOT]
+    link = ["-L", pkg, "-lint4linear_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../int4linear_b200"]
+    packer = os.path.join(REFERENCE_ROOT, "utils", "packer.cpp")
+    for name, src in [("test_correctness_dropin", "test/test_correctness.cu"),
+                      ("benchmark_dropin", "test/benchmark.cu")]:
+        out = os.path.join(out_dir, name)
+        srcs = [os.path.join(REFERENCE_ROOT, src), packer]
+        deps = srcs + [lib, os.path.join(pkg, "compat", "kernels", "linear_v21.h")]
+        if force or not _newer(out, deps):
+            subprocess.run(common + srcs + link + ["-o", out], check=True)
+        built.append(out)
+    return built
+
+
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
     print(build_ref(force))
+    print(build_dropin(force))

@@ -22,6 +22,7 @@ def _built():
     from int4linear_b200 import build as lbuild
     if lbuild.needs_build():
         lbuild.build()
+    lbuild.build_compat_check()
 
 
 def golden_files():
