@@ -27,3 +27,26 @@ def test_reference_correctness_program_runs_unchanged(cuda):
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "CUDA FAILED" not in r.stdout + r.stderr
+
+
+def test_reference_gpu_kernel_agrees(cuda):
+    """The reference's own GPU kernel (unmodified sources, sm_100a build in oracle/_ref), this
+    library and the CPU oracle must give the same int32 matrix."""
+    import numpy as np
+    import torch
+    import int4linear_b200 as L
+    from conftest import make_case
+    from oracle import oracle as O
+    ref = O.ref_lib()
+    if ref is None:
+        pytest.skip("built only where the reference checkout is available")
+    m, n, k = 512, 384, 1024
+    x, w, xp, wp = make_case(m, n, k, seed=12)
+    xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+    y_ref_gpu = torch.empty((m, n), dtype=torch.int32, device=cuda)
+    ref.ref_linear_v21_launch(xd.data_ptr(), wd.data_ptr(), y_ref_gpu.data_ptr(), m, n, k)
+    y_ours = L.linear(xd, wd)
+    torch.cuda.synchronize()
+    want = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+    assert O.is_same(y_ref_gpu.cpu().numpy(), want)
+    assert O.is_same(y_ours.cpu().numpy(), want)
