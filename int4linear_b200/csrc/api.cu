@@ -91,7 +91,8 @@ int forced_pairs()
     int v = g_pairs.load();
     if (v == -2) {
         const char* e = std::getenv("INT4L_PAIRS");
-        v = e ? (std::atoi(e) != 0 ? 1 : 0) : -1;
+        v = e ? std::atoi(e) : -1;
+        if (v < -1 || v > 2) v = -1;
         g_pairs.store(v);
     }
     return v;
@@ -135,6 +136,7 @@ DeviceCtx* current_ctx(int* status)
     c->encode_tiled = fn;
 
     int rc = setup_tcgen05(c);
+    if (rc == INT4L_OK) rc = setup_tcgen05_ts(c);
     if (rc == INT4L_OK) rc = setup_skinny(c);
     if (rc != INT4L_OK) { *status = rc; return nullptr; }
     c->attrs_set = true;
@@ -145,7 +147,7 @@ DeviceCtx* current_ctx(int* status)
 
 int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int elem_bytes,
                        uint64_t inner_elems, uint64_t rows, uint64_t row_pitch_bytes,
-                       uint32_t box_inner, uint32_t box_rows, bool swizzle128)
+                       uint32_t box_inner, uint32_t box_rows, bool swizzle128, bool swizzle64)
 {
     const cuuint64_t dims[2] = {inner_elems, rows};
     const cuuint64_t strides[1] = {row_pitch_bytes};
@@ -154,7 +156,7 @@ int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int e
     CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
         out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? INT4L_OK : INT4L_ERR_CUDA;
 }
@@ -304,7 +306,7 @@ int int4_linear_set_path(int path)
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
 {
     if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return INT4L_ERR_INVALID_ARG;
-    if (cta_pairs < -1 || cta_pairs > 1) return INT4L_ERR_INVALID_ARG;
+    if (cta_pairs < -1 || cta_pairs > 2) return INT4L_ERR_INVALID_ARG;
     g_tile_n.store(tile_n);
     g_direct_store.store(direct_store ? 1 : 0);
     g_pairs.store(cta_pairs);

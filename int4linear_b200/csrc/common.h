@@ -45,18 +45,21 @@ DeviceCtx* current_ctx(int* status);
 
 // Builds a 2-D tiled tensor map over a row-major byte/word matrix.
 //   elem_bytes 1 -> UINT8 elements, 4 -> INT32 elements.
-//   swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (inner box must be 128 B).
+//   swizzle128 selects CU_TENSOR_MAP_SWIZZLE_128B (inner box must be 128 B),
+//   swizzle64 CU_TENSOR_MAP_SWIZZLE_64B (inner box 64 B).
 int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int elem_bytes,
                        uint64_t inner_elems, uint64_t rows, uint64_t row_pitch_bytes,
-                       uint32_t box_inner, uint32_t box_rows, bool swizzle128);
+                       uint32_t box_inner, uint32_t box_rows, bool swizzle128, bool swizzle64 = false);
 
 // Kernel launchers.  Each returns an INT4L_* status; none of them synchronises.
 int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+int launch_tcgen05_ts(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);  // X operand in tensor memory
 int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 int launch_legacy(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 
 // One-off function attribute set-up (dynamic shared memory opt-in).
 int setup_tcgen05(DeviceCtx* ctx);
+int setup_tcgen05_ts(DeviceCtx* ctx);
 int setup_skinny(DeviceCtx* ctx);
 
 // Launch counter (kernels of this library launched by this process).
@@ -69,6 +72,6 @@ bool skinny_supports(const DeviceCtx* ctx, const Problem& p);
 // Experiment knobs (int4_linear_set_tuning / INT4L_EPILOGUE, INT4L_TILE_N).
 bool getenv_flag_direct_store();
 int forced_tile_n();
-int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always
+int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 pairs with both operands in smem, 2 pairs with X in TMEM
 
 }  // namespace i4l

@@ -43,24 +43,8 @@
 #include "common.h"
 #include "ptx.cuh"
 
-// Optional timeline capture (compile with -DI4L_TRACE): the first worker records a clock
-// value at the hand-over points of each role for its first kTraceIters K blocks.  Off in
-// normal builds; exists to find where a pipeline stalls.
-#ifdef I4L_TRACE
-constexpr int kTraceIters = 192;
-__device__ long long i4l_trace_buf[2][5][kTraceIters][4];
-#define I4L_TRACE_PUT(role, it, slot)                                                         \
-    do {                                                                                      \
-        if (worker == 0 && (it) < kTraceIters) i4l_trace_buf[cta_rank][role][it][slot] = clock64(); \
-    } while (0)
-extern "C" int int4_linear_debug_trace(void* dst, int bytes)
-{
-    if (bytes > static_cast<int>(sizeof(i4l_trace_buf))) bytes = sizeof(i4l_trace_buf);
-    return cudaMemcpyFromSymbol(dst, i4l_trace_buf, bytes) == cudaSuccess ? bytes : -1;
-}
-#else
-#define I4L_TRACE_PUT(role, it, slot) do { } while (0)
-#endif
+#define I4L_TRACE_EXPORT int4_linear_debug_trace
+#include "trace.cuh"
 
 namespace i4l {
 
@@ -239,7 +223,10 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             const int col0 = tn * BN;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32, ++chunk_no) {
+            for (int c = 0; c < BN; c += 32) {
+                // A chunk entirely outside Y is skipped as a whole, so that the staging buffers
+                // alternate exactly with the store groups that were committed.
+                if (kTmaStore && !(row0 < m && col0 + c < n)) continue;
                 uint32_t v[32];
                 tmem_ld_32x32(t_addr + c, v);
                 tmem_ld_wait();
@@ -256,10 +243,11 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                                make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0 && row0 < m && col0 + c < n) {
+                    if (lane == 0) {
                         tma_store_2d(&tm_y, stg, col0 + c, row0);
                         tma_store_commit();
                     }
+                    ++chunk_no;
                 } else {
                     if (row < m) {
                         int* dst = y + static_cast<size_t>(row) * n + col0 + c;
@@ -470,6 +458,7 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     bool pairs = p.m > 128 && pair_tiles >= ctx->max_pairs;
     if (forced != 0) pairs = false;
     if (forced_pairs() >= 0) pairs = forced_pairs() != 0;
+    if (pairs && forced_pairs() == 2) return launch_tcgen05_ts(ctx, p, stream);
     if (pairs) return tma_store ? launch_cfg<Cfg256x2, true>(ctx, p, stream) : launch_cfg<Cfg256x2, false>(ctx, p, stream);
     if (bn == 256) return tma_store ? launch_cfg<Cfg256, true>(ctx, p, stream) : launch_cfg<Cfg256, false>(ctx, p, stream);
     if (bn == 128) return tma_store ? launch_cfg<Cfg128, true>(ctx, p, stream) : launch_cfg<Cfg128, false>(ctx, p, stream);

@@ -33,6 +33,8 @@ VARIANTS = [
     ("tcgen05-64-direct", dict(path=L.PATH_TCGEN05, tile_n=64, direct=True)),
     ("tcgen05-pairs-tma", dict(path=L.PATH_TCGEN05, pairs=1)),
     ("tcgen05-pairs-direct", dict(path=L.PATH_TCGEN05, pairs=1, direct=True)),
+    ("tcgen05-pairs-xtmem-tma", dict(path=L.PATH_TCGEN05, pairs=2)),
+    ("tcgen05-pairs-xtmem-direct", dict(path=L.PATH_TCGEN05, pairs=2, direct=True)),
     ("legacy", dict(path=L.PATH_LEGACY)),
     ("auto", dict(path=L.PATH_AUTO)),
 ]
@@ -56,6 +58,8 @@ def test_golden_vectors(cuda, path, vname, variant):
 TAIL_SHAPES = [
     (1, 2, 32), (16, 130, 96), (17, 14, 128), (255, 258, 160), (257, 130, 32),
     (128, 256, 128), (129, 257, 224), (300, 77, 416), (64, 1000, 1056), (384, 512, 2048),
+    # several output chunks of the last tile fall outside Y (staging-buffer rotation)
+    (1024, 1024, 1024), (520, 36, 256),
 ]
 
 

@@ -71,7 +71,7 @@ def test_argument_checks_need_no_gpu():
     assert lib.int4_linear_launch_async(base + 4, base, base, 8, 8, 32, None) == 3
     assert lib.int4_linear_status_string(2).decode().startswith("unsupported")
     assert lib.int4_linear_set_tuning(100, 0, -1) == 1
-    assert lib.int4_linear_set_tuning(0, 0, 2) == 1
+    assert lib.int4_linear_set_tuning(0, 0, 3) == 1
     assert lib.int4_linear_set_tuning(0, 0, -1) == 0
 
 
