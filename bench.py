@@ -303,27 +303,36 @@ def main():
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
+    pipelined = None
     if rotate:
         # A single ~5 us launch is below what an event pair (or a Python call) resolves, so the K
         # steps are captured into one CUDA graph -- K launches, each on its own copy of W -- and
-        # the replay is timed as a whole.
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(args.steps):
-                    step(i)
-        torch.cuda.current_stream().wait_stream(side)
-        launches0 = L.launch_count() - args.steps  # the capture issued the K launches
-        graph.replay()
-        barrier()
-        flush.zero_()
-        starts[0].record()
-        graph.replay()
-        ends[0].record()
-        barrier()
-        total_ms = starts[0].elapsed_time(ends[0])
+        # the replay is timed as a whole.  `value` is measured with ordinary launches (each waits
+        # for the previous one); the same graph is then re-captured with the library's launch
+        # overlap modes (programmatic dependent launch) and reported under "pipelined".
+        def graph_ms(mode):
+            L.set_overlap(mode)
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(args.steps):
+                        step(i)
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            barrier()
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            barrier()
+            L.set_overlap(0)
+            return e0.elapsed_time(e1)
+        total_ms = graph_ms(0)
+        pipelined = {f"overlap_{mode}": graph_ms(mode) / args.steps for mode in (1, 2)}
+        launches0 = L.launch_count() - args.steps  # the timed replay ran the K captured launches
     else:
         for i in range(args.steps):
             flush.zero_()  # evict operands and result from L2 (test/benchmark.cu:93-96)
@@ -425,6 +434,13 @@ def main():
                        else {1: "tcgen05", 2: "legacy", 3: "skinny"}[L.path_for(m, n_local, k)]},
             "tops": tops, "algorithmic_gbs": gbs,
             "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline}
+    if pipelined is not None:
+        line["pipelined"] = {
+            name: {"ms_per_step": ms, "GB/s": alg_bytes_local * world / (ms * 1e-3) / 1e9,
+                   "frac_of_hbm_peak": alg_bytes_local / (ms * 1e-3) / 1e9 / float(peaks["hbm_gbs"])}
+            for name, ms in pipelined.items()}
+        line["pipelined"]["note"] = ("back-to-back launches with int4_linear_set_overlap: 1 = weights not written "
+                                     "by preceding work, 2 = weights and X; `value` uses ordinary launches")
     if e2e is not None:
         line["e2e"] = e2e
     if gather_ms is not None:

@@ -101,6 +101,16 @@ int int4_linear_set_path(int path);
  * Environment: INT4L_TILE_N, INT4L_EPILOGUE=direct, INT4L_PAIRS. */
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
 
+/* Overlap of back-to-back decode-shape launches in one stream (programmatic dependent
+ * launch).  0 (default): every launch waits for the preceding work in its stream, as any
+ * kernel does.  1: the caller promises that the WEIGHTS passed to a launch are not written by
+ * the work queued before it in the stream (stationary weights): the launch may start early
+ * and prefetch weights while its predecessor finishes; X is read and Y written only after
+ * the predecessor has completed.  2: the same promise for the weights AND X.
+ * Returns the previous mode, or -INT4L_ERR_INVALID_ARG.  Environment: INT4L_OVERLAP.
+ * No reference counterpart (the reference launcher synchronises the device after every call). */
+int int4_linear_set_overlap(int mode);
+
 /* Which family the dispatcher would use for a shape (INT4L_PATH_*). */
 int int4_linear_path_for(int m, int n, int k);
 

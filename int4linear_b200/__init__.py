@@ -19,6 +19,7 @@ from .linear import (  # noqa: F401
     launch_count,
     path_for,
     set_path,
+    set_overlap,
     set_tuning,
     PATH_AUTO,
     PATH_TCGEN05,

@@ -17,6 +17,7 @@ SYMBOLS = {
     "int4_linear_status_string": (ctypes.c_char_p, [_I]),
     "int4_linear_set_path": (_I, [_I]),
     "int4_linear_set_tuning": (_I, [_I, _I, _I]),
+    "int4_linear_set_overlap": (_I, [_I]),
     "int4_linear_path_for": (_I, [_I, _I, _I]),
     "int4_linear_device_info": (_I, [_I]),
     "int4_linear_launch_count": (_LL, []),

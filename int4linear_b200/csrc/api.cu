@@ -21,6 +21,7 @@ std::atomic<long long> g_launches{0};
 std::atomic<int> g_path{-1};       // -1 = not yet read from the environment
 std::atomic<int> g_tile_n{0};      // 0 = automatic
 std::atomic<int> g_direct_store{-1};
+std::atomic<int> g_overlap{-1};    // -1 = not yet read from the environment
 std::atomic<int> g_pairs{-2};      // -2 = not yet read from the environment
 thread_local int t_last_status = INT4L_OK;
 
@@ -82,6 +83,18 @@ int forced_tile_n()
     if (v == 0) {
         const char* e = std::getenv("INT4L_TILE_N");
         if (e) v = std::atoi(e);
+    }
+    return v;
+}
+
+int stream_overlap_mode()
+{
+    int v = g_overlap.load();
+    if (v < 0) {
+        const char* e = std::getenv("INT4L_OVERLAP");
+        v = e ? std::atoi(e) : 0;
+        if (v < 0 || v > 2) v = 0;
+        g_overlap.store(v);
     }
     return v;
 }
@@ -311,6 +324,14 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
     g_direct_store.store(direct_store ? 1 : 0);
     g_pairs.store(cta_pairs);
     return INT4L_OK;
+}
+
+int int4_linear_set_overlap(int mode)
+{
+    if (mode < 0 || mode > 2) return -INT4L_ERR_INVALID_ARG;
+    const int prev = stream_overlap_mode();
+    g_overlap.store(mode);
+    return prev;
 }
 
 int int4_linear_path_for(int m, int n, int k)

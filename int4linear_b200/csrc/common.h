@@ -72,6 +72,7 @@ bool skinny_supports(const DeviceCtx* ctx, const Problem& p);
 // Experiment knobs (int4_linear_set_tuning / INT4L_EPILOGUE, INT4L_TILE_N).
 bool getenv_flag_direct_store();
 int forced_tile_n();
+int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
 int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 pairs with both operands in smem, 2 pairs with X in TMEM
 
 }  // namespace i4l

@@ -168,12 +168,17 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
 // ALU operations to expand it, four MMAs.  Weight loads for several groups ahead are kept
 // in flight, and the first of them are issued before anything else happens in the kernel,
 // so HBM is busy from the first cycle; X never goes through shared memory.
-template <int KBW>
-__global__ void __launch_bounds__(kSkinnyThreads, 1)
+template <int KBW, int D, int MINB>
+__global__ void __launch_bounds__(kSkinnyThreads, MINB)
 gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
-                          int m, int n, int k, int groups_total)
+                          int m, int n, int k, int groups_total, int overlap)
 {
-    constexpr int D = 8 / KBW;  // groups of loads in flight per warp
+    // D = groups of weight loads in flight per warp.
+    // overlap: 0 = ordinary launch.  1, 2 = launched with programmatic stream serialisation:
+    // this grid may start while the preceding work in the stream is still running, and lets its
+    // own successor do the same.  Everything it reads before griddepcontrol.wait must therefore
+    // not be written by that preceding work: the weights (1), or the weights and X (2).
+    if (overlap) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) uint8_t smem[];
     int* acc = reinterpret_cast<int*>(smem);  // [groups][16][8]
 
@@ -202,6 +207,8 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
     uint4 wv[D][KBW];
 #pragma unroll
     for (int d = 0; d < D; ++d) load_group(d, wv[d]);
+
+    if (overlap == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // X fragments of this warp's K slice: rows g and g + 8, expanded to bytes.
     uint32_t a[KBW][4][4];
@@ -251,6 +258,7 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
     }
     __syncthreads();
 
+    if (overlap == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int cols = n_groups * 8;
     const int col_base = g_begin * 8;
     for (int i = tid; i < m * cols; i += kSkinnyThreads) {
@@ -444,9 +452,9 @@ int setup_skinny(DeviceCtx*)
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<1, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<2, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<4, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     return e == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }
 
@@ -459,15 +467,35 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     int* y = static_cast<int*>(p.y);
     const int kb_count = (p.k + 127) / 128;
     if (p.m <= 16 && kb_count >= 16 && kb_count <= 64 && skinny_variant() != 2 && skinny_variant() != 3) {
-        const size_t smem = static_cast<size_t>(s.groups_per_cta_max) * 128 * sizeof(int);
+        // Two CTAs per SM: consecutive launches (overlap modes) can then be resident together,
+        // so one launch streams weights while the previous one merges and writes its result.
+        const int overlap = stream_overlap_mode();
+        // One CTA per SM when launches may fully overlap (two launches then share each SM);
+        // otherwise two, which hides more latency inside a single launch.
+        int ctas_per_sm = overlap == 2 ? 1 : 2;
+        if (const char* e = getenv("INT4L_SKINNY_CTAS_PER_SM")) ctas_per_sm = atoi(e) == 1 ? 1 : 2;
+        const int grid = s.groups_total < ctas_per_sm * ctx->sm_count ? s.groups_total : ctas_per_sm * ctx->sm_count;
+        const int per_cta = (s.groups_total + grid - 1) / grid;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid, 1, 1);
+        cfg.blockDim = dim3(kSkinnyThreads, 1, 1);
+        cfg.dynamicSmemBytes = static_cast<size_t>(per_cta) * 128 * sizeof(int);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = overlap ? 1 : 0;
+        cudaError_t e;
         if (kb_count <= 16)
-            gemm_s4_skinny_reg_kernel<1><<<s.grid, kSkinnyThreads, smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<1, 4, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap);
         else if (kb_count <= 32)
-            gemm_s4_skinny_reg_kernel<2><<<s.grid, kSkinnyThreads, smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<2, 2, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap);
         else
-            gemm_s4_skinny_reg_kernel<4><<<s.grid, kSkinnyThreads, smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<4, 2, 1>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap);
         count_launch();
-        return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+        if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+        return INT4L_OK;
     }
     if (p.m <= 16 && p.k >= 256 && skinny_variant() != 2) {
         // Whole slab resident when it fits (one buffer per warp holding every row of the CTA's

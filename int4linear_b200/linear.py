@@ -145,6 +145,14 @@ def set_tuning(tile_n: int = 0, direct_store: bool = False, cta_pairs: int = -1)
         raise Int4LinearError(st, "int4_linear_set_tuning")
 
 
+def set_overlap(mode: int) -> int:
+    """0 off, 1 weights stationary, 2 weights and X stationary (see int4_linear_set_overlap)."""
+    r = _lib.load().int4_linear_set_overlap(mode)
+    if r < 0:
+        raise Int4LinearError(-r, "int4_linear_set_overlap")
+    return r
+
+
 def path_for(m: int, n: int, k: int) -> int:
     r = _lib.load().int4_linear_path_for(m, n, k)
     if r < 0:

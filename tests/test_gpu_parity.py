@@ -148,3 +148,31 @@ def test_tensor_front_end(cuda):
     torch.cuda.synchronize()
     assert L.last_status() == 0
     assert O.is_same(y.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_overlapped_launches_stay_exact(cuda, mode):
+    """Back-to-back decode launches with programmatic dependent launch enabled: every launch of the
+    chain must still produce the exact result (distinct weights per launch, one shared Y buffer that
+    each launch overwrites, and a result snapshot taken between launches on the same stream)."""
+    import torch
+    m, n, k = 16, 2368, 4096
+    x = L.uniform_s4(31, m, k)
+    xd = torch.from_numpy(L.pack_bytes(x)).to(cuda)
+    ws = [L.uniform_s4(40 + i, n, k) for i in range(4)]
+    wds = [torch.from_numpy(L.pack_bytes(w)).to(cuda) for w in ws]
+    yd = torch.empty((m, n), dtype=torch.int32, device=cuda)
+    prev = L.set_overlap(mode)
+    try:
+        outs = []
+        for rep in range(3):
+            for wd in wds:
+                L.linear(xd, wd, out=yd)
+                outs.append(yd.clone())
+        torch.cuda.synchronize()
+    finally:
+        L.set_overlap(prev)
+    assert L.last_status() == 0
+    refs = [O.linear_ref_sgemm(x, w) for w in ws]
+    for i, out in enumerate(outs):
+        assert O.is_same(out.cpu().numpy(), refs[i % 4]), f"launch {i}"
