@@ -67,6 +67,16 @@ int int4_linear_launch_async(const void* x_packed_d, const void* w_packed_d, voi
                              int m, int n, int k, void* stream);
 
 /*
+ * The operator with a fused bias: Y[i][j] = sum_l X[i][l] * W[j][l] + bias[j], all int32 and
+ * exact.  bias_d is a device pointer to n ints (NULL = no bias, identical to
+ * int4_linear_launch_async).  No reference counterpart: the reference lists bias addition as
+ * future work (README.md:72); the add happens in the kernels' epilogue, so Y is still written
+ * exactly once.
+ */
+int int4_linear_bias_launch_async(const void* x_packed_d, const void* w_packed_d, const int* bias_d,
+                                  void* y_d, int m, int n, int k, void* stream);
+
+/*
  * Host-buffer form of the call sequence in test/test_correctness.cu:53-63
  * (cudaMalloc x3, cudaMemcpy H2D x2, launch, cudaMemcpy D2H): operands and
  * result live in host memory; the library stages them through device buffers
@@ -77,6 +87,18 @@ int int4_linear_launch_async(const void* x_packed_d, const void* w_packed_d, voi
  */
 int int4_linear_host(const void* x_packed_h, const void* w_packed_h, void* y_h,
                      int m, int n, int k, int w_resident);
+
+/*
+ * Device-side forms of `void pack(const int* src, int* dst, int m, int n)` and
+ * `void unpack(...)` (utils/packer.h:5-6, utils/packer.cpp:3-31): same bit layout, same
+ * row padding to a multiple of eight elements, but source and destination are DEVICE
+ * pointers and the work is a kernel on `stream`.  rows/cols take the place of the
+ * reference's m/n.  dst of pack (src of unpack) holds rows * ceil(cols/8) 32-bit words.
+ * int4_linear_pack_i8 takes one signed byte per element instead of one int.
+ */
+int int4_linear_pack_i32(const int* src_d, void* dst_d, int rows, int cols, void* stream);
+int int4_linear_pack_i8(const signed char* src_d, void* dst_d, int rows, int cols, void* stream);
+int int4_linear_unpack_i32(const void* src_d, int* dst_d, int rows, int cols, void* stream);
 
 /* Status of the most recent call on the current device; also polls the word
  * the kernels raise when a bounded wait expires (and clears it). */

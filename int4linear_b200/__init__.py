@@ -7,7 +7,7 @@ seeded operand generator, and the N-sharding driver for several GPUs.  There is
 no CPU implementation of the operator here; without the library or without a
 B200 the compute calls raise.
 """
-from .packer import pack, unpack, pack_bytes, unpack_bytes  # noqa: F401
+from .packer import pack, unpack, pack_bytes, unpack_bytes, pack_device, unpack_device  # noqa: F401
 from .data import uniform_s4, uniform_s4_packed  # noqa: F401
 from .linear import (  # noqa: F401
     LinearArgs,

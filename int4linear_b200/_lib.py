@@ -12,7 +12,11 @@ _VP, _I, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 SYMBOLS = {
     "int4_linear_launch": (None, [_VP, _VP, _VP, _I, _I, _I]),
     "int4_linear_launch_async": (_I, [_VP, _VP, _VP, _I, _I, _I, _VP]),
+    "int4_linear_bias_launch_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),
+    "int4_linear_pack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
+    "int4_linear_pack_i8": (_I, [_VP, _VP, _I, _I, _VP]),
+    "int4_linear_unpack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_last_status": (_I, []),
     "int4_linear_status_string": (ctypes.c_char_p, [_I]),
     "int4_linear_set_path": (_I, [_I]),

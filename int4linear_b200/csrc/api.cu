@@ -235,6 +235,19 @@ int int4_linear_launch_async(const void* x, const void* w, void* y, int m, int n
     return rc;
 }
 
+int int4_linear_bias_launch_async(const void* x, const void* w, const int* bias_d, void* y, int m, int n, int k, void* stream)
+{
+    int rc = check_args(x, w, y, m, n, k);
+    if (rc == INT4L_OK && bias_d != nullptr && (reinterpret_cast<uintptr_t>(bias_d) & 3u)) rc = INT4L_ERR_MISALIGNED;
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{x, w, y, m, n, k, bias_d};
+    rc = dispatch(ctx, p, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
 void int4_linear_launch(void* x, void* w, void* y, int m, int n, int k)
 {
     int rc = int4_linear_launch_async(x, w, y, m, n, k, nullptr);
@@ -278,6 +291,36 @@ int int4_linear_host(const void* x_h, const void* w_h, void* y_h, int m, int n, 
         if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
     }
     rc = poll_device_status(ctx);
+    t_last_status = rc;
+    return rc;
+}
+
+int int4_linear_pack_i32(const int* src_d, void* dst_d, int rows, int cols, void* stream)
+{
+    if (!src_d || !dst_d || rows <= 0 || cols <= 0) { t_last_status = INT4L_ERR_INVALID_ARG; return INT4L_ERR_INVALID_ARG; }
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (ctx) rc = launch_pack(ctx, src_d, 4, dst_d, rows, cols, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
+int int4_linear_pack_i8(const signed char* src_d, void* dst_d, int rows, int cols, void* stream)
+{
+    if (!src_d || !dst_d || rows <= 0 || cols <= 0) { t_last_status = INT4L_ERR_INVALID_ARG; return INT4L_ERR_INVALID_ARG; }
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (ctx) rc = launch_pack(ctx, src_d, 1, dst_d, rows, cols, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
+int int4_linear_unpack_i32(const void* src_d, int* dst_d, int rows, int cols, void* stream)
+{
+    if (!src_d || !dst_d || rows <= 0 || cols <= 0) { t_last_status = INT4L_ERR_INVALID_ARG; return INT4L_ERR_INVALID_ARG; }
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (ctx) rc = launch_unpack(ctx, src_d, dst_d, rows, cols, static_cast<cudaStream_t>(stream));
     t_last_status = rc;
     return rc;
 }

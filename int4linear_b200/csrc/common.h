@@ -18,6 +18,9 @@ struct Problem {
     const void* w;
     void* y;
     int m, n, k;
+    // Optional int32 bias of length N added to every row of Y (nullptr = none).  Not part of the
+    // reference operator (its README lists bias as future work); exact integer arithmetic.
+    const int* bias = nullptr;
 };
 
 // Per-device state created on the first call on that device.
@@ -56,6 +59,10 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 int launch_tcgen05_ts(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);  // X operand in tensor memory
 int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 int launch_legacy(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+
+// Device-side packer (packer.cu).  src_elem_bytes: 4 = int32 per element, 1 = int8.
+int launch_pack(DeviceCtx* ctx, const void* src, int src_elem_bytes, void* dst, int rows, int cols, cudaStream_t stream);
+int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols, cudaStream_t stream);
 
 // One-off function attribute set-up (dynamic shared memory opt-in).
 int setup_tcgen05(DeviceCtx* ctx);

@@ -22,7 +22,7 @@ __device__ __forceinline__ void mma_s4(int (&c)[4], uint32_t a0, uint32_t a1, ui
 // 4 warps as 2 x 2; each warp computes 32 x 32 outputs = 2 x 4 MMA tiles.
 __global__ void __launch_bounds__(128)
 gemm_s4_legacy_kernel(const uint32_t* __restrict__ x, const uint32_t* __restrict__ w, int* __restrict__ y,
-                      int m, int n, int k)
+                      int m, int n, int k, const int* __restrict__ bias)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, q = lane & 3;
@@ -73,6 +73,10 @@ gemm_s4_legacy_kernel(const uint32_t* __restrict__ x, const uint32_t* __restrict
         for (int j = 0; j < 4; ++j) {
             const int c = col0 + j * 8 + 2 * q;
             const int r_lo = row0 + i * 16 + g, r_hi = r_lo + 8;
+            if (bias != nullptr) {
+                const int b0 = c < n ? __ldg(bias + c) : 0, b1 = c + 1 < n ? __ldg(bias + c + 1) : 0;
+                acc[i][j][0] += b0; acc[i][j][1] += b1; acc[i][j][2] += b0; acc[i][j][3] += b1;
+            }
             if (r_lo < m) {
                 if (c < n) y[static_cast<size_t>(r_lo) * n + c] = acc[i][j][0];
                 if (c + 1 < n) y[static_cast<size_t>(r_lo) * n + c + 1] = acc[i][j][1];
@@ -91,7 +95,7 @@ int launch_legacy(DeviceCtx*, const Problem& p, cudaStream_t stream)
     dim3 grid((p.n + 63) / 64, (p.m + 63) / 64);
     gemm_s4_legacy_kernel<<<grid, 128, 0, stream>>>(static_cast<const uint32_t*>(p.x),
                                                      static_cast<const uint32_t*>(p.w),
-                                                     static_cast<int*>(p.y), p.m, p.n, p.k);
+                                                     static_cast<int*>(p.y), p.m, p.n, p.k, p.bias);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }

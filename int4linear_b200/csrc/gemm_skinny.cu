@@ -55,7 +55,7 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 template <int MB>
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
-                      int m, int n, int k, int groups_total, int groups_per_cta_max, int x_pitch)
+                      int m, int n, int k, int groups_total, int groups_per_cta_max, int x_pitch, const int* __restrict__ bias)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* xs = smem;                                                  // [MB*16][x_pitch]
@@ -156,7 +156,7 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
     for (int i = tid; i < m * cols; i += kSkinnyThreads) {
         const int r = i / cols, cc = i - r * cols;
         const int col = col_base + cc;
-        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * MB * 16 + r) * 8 + (cc & 7)];
+        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * MB * 16 + r) * 8 + (cc & 7)] + (bias ? __ldg(bias + col) : 0);
     }
 }
 
@@ -171,7 +171,7 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
 template <int KBW, int D, int MINB>
 __global__ void __launch_bounds__(kSkinnyThreads, MINB)
 gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
-                          int m, int n, int k, int groups_total, int overlap)
+                          int m, int n, int k, int groups_total, int overlap, const int* __restrict__ bias)
 {
     // D = groups of weight loads in flight per warp.
     // overlap: 0 = ordinary launch.  1, 2 = launched with programmatic stream serialisation:
@@ -264,7 +264,7 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
     for (int i = tid; i < m * cols; i += kSkinnyThreads) {
         const int r = i / cols, cc = i - r * cols;
         const int col = col_base + cc;
-        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)];
+        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)] + (bias ? __ldg(bias + col) : 0);
     }
 }
 
@@ -286,7 +286,7 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_s4_skinny_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const uint8_t* __restrict__ x,
                           int* __restrict__ y, int m, int n, int k, int groups_total,
-                          int stage_rows, int n_buffers, int* status)
+                          int stage_rows, int n_buffers, int* status, const int* __restrict__ bias)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -397,7 +397,7 @@ gemm_s4_skinny_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const uint8_
     for (int i = tid; i < m * cols; i += kSkinnyThreads) {
         const int r = i / cols, cc = i - r * cols;
         const int col = col_base + cc;
-        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)];
+        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)] + (bias ? __ldg(bias + col) : 0);
     }
 }
 
@@ -488,11 +488,11 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         cfg.numAttrs = overlap ? 1 : 0;
         cudaError_t e;
         if (kb_count <= 16)
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<1, 4, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<1, 4, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias);
         else if (kb_count <= 32)
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<2, 2, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<2, 2, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias);
         else
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<4, 2, 1>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<4, 2, 1>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias);
         count_launch();
         if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
         return INT4L_OK;
@@ -520,17 +520,17 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
             int rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, 128, stage_rows, true);
             if (rc != INT4L_OK) return rc;
             gemm_s4_skinny_tma_kernel<<<s.grid, kSkinnyThreads, smem, stream>>>(
-                tm_w, x, y, p.m, p.n, p.k, s.groups_total, stage_rows, n_buffers, ctx->status_dev);
+                tm_w, x, y, p.m, p.n, p.k, s.groups_total, stage_rows, n_buffers, ctx->status_dev, p.bias);
             count_launch();
             return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
         }
     }
     if (s.mb == 1)
-        gemm_s4_skinny_kernel<1><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch);
+        gemm_s4_skinny_kernel<1><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias);
     else if (s.mb == 2)
-        gemm_s4_skinny_kernel<2><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch);
+        gemm_s4_skinny_kernel<2><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias);
     else
-        gemm_s4_skinny_kernel<4><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch);
+        gemm_s4_skinny_kernel<4><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }

@@ -60,7 +60,7 @@ gemm_s4_tcgen05_ts_kernel(const __grid_constant__ CUtensorMap tm_x,
                           const __grid_constant__ CUtensorMap tm_w,
                           const __grid_constant__ CUtensorMap tm_y,
                           int* __restrict__ y, int m, int n, int k,
-                          int tiles_m, int tiles_n, int* status)
+                          int tiles_m, int tiles_n, int* status, const int* __restrict__ bias)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -193,6 +193,11 @@ gemm_s4_tcgen05_ts_kernel(const __grid_constant__ CUtensorMap tm_x,
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = static_cast<uint32_t>(static_cast<int>(v[i]) >> 8);
+                if (bias != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + c + i < n) v[i] += static_cast<uint32_t>(__ldg(bias + col0 + c + i));
+                }
                 if constexpr (kTmaStore) {
                     const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
                     if (lane == 0) tma_store_wait_read<1>();
@@ -358,7 +363,7 @@ int launch_ts_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_ts_kernel<kTmaStore>, tm_x, tm_w, tm_y,
-                                       static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, ctx->status_dev);
+                                       static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, ctx->status_dev, p.bias);
     count_launch();
     if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
     return INT4L_OK;

@@ -1,0 +1,109 @@
+// Device-side nibble packer: the reference's host functions
+//     void pack  (const int* src, int* dst, int m, int n)   utils/packer.cpp:3-18
+//     void unpack(const int* src, int* dst, int m, int n)   utils/packer.cpp:20-31
+// as HBM-bound kernels, so that operands produced on the GPU never have to visit the host
+// to be packed.  Bit layout identical: element 8j+t of a row in bits [4t, 4t+4) of word j,
+// rows padded with zero nibbles to a multiple of eight elements, unpack sign-extends.
+// A second packer takes int8 sources (the natural output type of a quantiser).
+//
+// One thread produces one 32-bit packed word (pack) or consumes one (unpack); consecutive
+// threads touch consecutive words, so every access is coalesced; 16-byte vector loads/stores
+// are used whenever the row length keeps rows 16-byte aligned.
+#include "common.h"
+
+namespace i4l {
+
+namespace {
+
+constexpr int kPackThreads = 256;
+
+template <typename SrcT>
+__global__ void __launch_bounds__(kPackThreads)
+pack_s4_kernel(const SrcT* __restrict__ src, uint32_t* __restrict__ dst, int rows, int cols, int words_per_row)
+{
+    const long long total = static_cast<long long>(rows) * words_per_row;
+    const bool vec = (cols % 8) == 0 && (reinterpret_cast<uintptr_t>(src) % 16) == 0;
+    for (long long w = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; w < total;
+         w += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(w / words_per_row), j = static_cast<int>(w - static_cast<long long>(r) * words_per_row);
+        const SrcT* p = src + static_cast<size_t>(r) * cols + j * 8;
+        int e[8];
+        if (vec) {
+            if constexpr (sizeof(SrcT) == 4) {
+                const int4 a = __ldg(reinterpret_cast<const int4*>(p));
+                const int4 b = __ldg(reinterpret_cast<const int4*>(p) + 1);
+                e[0] = a.x; e[1] = a.y; e[2] = a.z; e[3] = a.w; e[4] = b.x; e[5] = b.y; e[6] = b.z; e[7] = b.w;
+            } else {
+                const int2 a = __ldg(reinterpret_cast<const int2*>(p));
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    e[t] = (a.x >> (8 * t)) & 0xFF;
+                    e[4 + t] = (a.y >> (8 * t)) & 0xFF;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) e[t] = (j * 8 + t < cols) ? static_cast<int>(p[t]) : 0;
+        }
+        uint32_t word = 0;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) word |= (static_cast<uint32_t>(e[t]) & 0xFu) << (4 * t);
+        dst[w] = word;
+    }
+}
+
+__global__ void __launch_bounds__(kPackThreads)
+unpack_s4_kernel(const uint32_t* __restrict__ src, int* __restrict__ dst, int rows, int cols, int words_per_row)
+{
+    const long long total = static_cast<long long>(rows) * words_per_row;
+    const bool vec = (cols % 8) == 0 && (reinterpret_cast<uintptr_t>(dst) % 16) == 0;
+    for (long long w = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; w < total;
+         w += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(w / words_per_row), j = static_cast<int>(w - static_cast<long long>(r) * words_per_row);
+        const uint32_t word = __ldg(src + w);
+        int e[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) e[t] = static_cast<int>(word << (28 - 4 * t)) >> 28;  // sign-extending nibble extract
+        int* p = dst + static_cast<size_t>(r) * cols + j * 8;
+        if (vec) {
+            reinterpret_cast<int4*>(p)[0] = make_int4(e[0], e[1], e[2], e[3]);
+            reinterpret_cast<int4*>(p)[1] = make_int4(e[4], e[5], e[6], e[7]);
+        } else {
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+                if (j * 8 + t < cols) p[t] = e[t];
+        }
+    }
+}
+
+int grid_for(const DeviceCtx* ctx, long long words)
+{
+    long long blocks = (words + kPackThreads - 1) / kPackThreads;
+    const long long cap = static_cast<long long>(ctx->sm_count) * 16;
+    return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace
+
+int launch_pack(DeviceCtx* ctx, const void* src, int src_elem_bytes, void* dst, int rows, int cols, cudaStream_t stream)
+{
+    const int wpr = (cols + 7) / 8;
+    const long long words = static_cast<long long>(rows) * wpr;
+    if (src_elem_bytes == 4)
+        pack_s4_kernel<int><<<grid_for(ctx, words), kPackThreads, 0, stream>>>(static_cast<const int*>(src), static_cast<uint32_t*>(dst), rows, cols, wpr);
+    else
+        pack_s4_kernel<signed char><<<grid_for(ctx, words), kPackThreads, 0, stream>>>(static_cast<const signed char*>(src), static_cast<uint32_t*>(dst), rows, cols, wpr);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols, cudaStream_t stream)
+{
+    const int wpr = (cols + 7) / 8;
+    const long long words = static_cast<long long>(rows) * wpr;
+    unpack_s4_kernel<<<grid_for(ctx, words), kPackThreads, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<int*>(dst), rows, cols, wpr);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+}  // namespace i4l

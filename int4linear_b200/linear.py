@@ -84,13 +84,14 @@ def launch(args: LinearArgs, stream=None) -> None:
         raise Int4LinearError(st, "int4_linear_launch_async")
 
 
-def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None):
-    """Y = X @ W^T for packed CUDA tensors.
+def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias=None):
+    """Y = X @ W^T (+ bias) for packed CUDA tensors.
 
     x_packed: [m, k/2] uint8 (or [m, k/8] int32) on a B200; w_packed likewise with n rows.
     Returns an [m, n] int32 CUDA tensor (written into `out` when given).  Asynchronous
     on the current torch stream; call last_status() after a synchronize to learn
-    about device-side failures."""
+    about device-side failures.  `bias`: optional CUDA int32 tensor [n], added to every row in the
+    kernel epilogue (exact)."""
     import torch
     if not (x_packed.is_cuda and w_packed.is_cuda):
         raise ValueError("linear() needs CUDA tensors; there is no CPU implementation")
@@ -104,7 +105,18 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None):
     if out is None:
         out = torch.empty((m, n), dtype=torch.int32, device=xb.device)
     with torch.cuda.device(xb.device):
-        launch(LinearArgs(xb.data_ptr(), wb.data_ptr(), out.data_ptr(), m, n, k), stream)
+        if bias is None:
+            launch(LinearArgs(xb.data_ptr(), wb.data_ptr(), out.data_ptr(), m, n, k), stream)
+        else:
+            if bias.dtype != torch.int32 or bias.numel() != n or not bias.is_cuda:
+                raise ValueError("bias must be a CUDA int32 tensor with n elements")
+            bias = bias.contiguous()
+            handle = (stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)) if stream is not None \
+                else torch.cuda.current_stream().cuda_stream
+            st = _lib.load().int4_linear_bias_launch_async(xb.data_ptr(), wb.data_ptr(), bias.data_ptr(),
+                                                           out.data_ptr(), m, n, k, handle)
+            if st != 0:
+                raise Int4LinearError(st, "int4_linear_bias_launch_async")
     return out
 
 

@@ -60,3 +60,46 @@ def unpack_bytes(packed: np.ndarray) -> np.ndarray:
     out[:, 0::2] = np.where(lo >= 8, lo - 16, lo)
     out[:, 1::2] = np.where(hi >= 8, hi - 16, hi)
     return out
+
+
+def pack_device(src, stream=None):
+    """Device-side pack: a CUDA tensor [m, n] of int32 or int8 values in [-8, 7] ->
+    CUDA int32 tensor [m, ceil(n/8)] in the reference's word layout (asynchronous)."""
+    import torch
+    from . import _lib
+    from .linear import Int4LinearError
+    if not src.is_cuda or src.dim() != 2:
+        raise ValueError("pack_device expects a 2-D CUDA tensor")
+    src = src.contiguous()
+    m, n = src.shape
+    dst = torch.empty((m, (n + 7) // 8), dtype=torch.int32, device=src.device)
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    lib = _lib.load()
+    with torch.cuda.device(src.device):
+        if src.dtype == torch.int32:
+            st = lib.int4_linear_pack_i32(src.data_ptr(), dst.data_ptr(), m, n, handle)
+        elif src.dtype == torch.int8:
+            st = lib.int4_linear_pack_i8(src.data_ptr(), dst.data_ptr(), m, n, handle)
+        else:
+            raise TypeError("pack_device takes int32 or int8 tensors")
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_pack")
+    return dst
+
+
+def unpack_device(src, n: int, stream=None):
+    """Device-side unpack: CUDA int32 words [m, ceil(n/8)] -> CUDA int32 tensor [m, n]."""
+    import torch
+    from . import _lib
+    from .linear import Int4LinearError
+    src = src.contiguous()
+    m = src.shape[0]
+    if src.dtype != torch.int32 or src.shape[1] != (n + 7) // 8:
+        raise ValueError("unpack_device expects int32 words [m, ceil(n/8)]")
+    dst = torch.empty((m, n), dtype=torch.int32, device=src.device)
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    with torch.cuda.device(src.device):
+        st = _lib.load().int4_linear_unpack_i32(src.data_ptr(), dst.data_ptr(), m, n, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_unpack_i32")
+    return dst

@@ -176,3 +176,30 @@ def test_overlapped_launches_stay_exact(cuda, mode):
     refs = [O.linear_ref_sgemm(x, w) for w in ws]
     for i, out in enumerate(outs):
         assert O.is_same(out.cpu().numpy(), refs[i % 4]), f"launch {i}"
+
+
+@pytest.mark.parametrize("shape,variant", [
+    ((300, 520, 256), dict(path=L.PATH_TCGEN05, pairs=1)),
+    ((300, 520, 256), dict(path=L.PATH_TCGEN05, pairs=2, direct=True)),
+    ((200, 77, 160), dict(path=L.PATH_TCGEN05, pairs=0)),
+    ((16, 1000, 4096), dict(path=L.PATH_SKINNY)),
+    ((40, 264, 1024), dict(path=L.PATH_SKINNY)),
+    ((9, 64, 96), dict(path=L.PATH_SKINNY)),
+    ((130, 70, 128), dict(path=L.PATH_LEGACY)),
+], ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else "-".join(f"{k}{x}" for k, x in v.items()))
+def test_fused_bias_is_exact(cuda, shape, variant):
+    import torch
+    m, n, k = shape
+    x, w, xp, wp = make_case(m, n, k, seed=21)
+    bias = (np.arange(n, dtype=np.int64) * 7919 % 200001 - 100000).astype(np.int32)
+    prev = L.set_path(variant.get("path", L.PATH_AUTO))
+    L.set_tuning(0, variant.get("direct", False), variant.get("pairs", -1))
+    try:
+        y = L.linear(torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda), bias=torch.from_numpy(bias).to(cuda))
+        torch.cuda.synchronize()
+    finally:
+        L.set_path(prev)
+        L.set_tuning(0, False, -1)
+    assert L.last_status() == 0
+    want = O.linear_ref(x.astype(np.int32), w.astype(np.int32)) + bias[None, :]
+    assert O.is_same(y.cpu().numpy(), want)
