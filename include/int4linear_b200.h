@@ -77,6 +77,20 @@ int int4_linear_bias_launch_async(const void* x_packed_d, const void* w_packed_d
                                   void* y_d, int m, int n, int k, void* stream);
 
 /*
+ * Weight-stationary pre-layout.  int4_linear_prepare_weights expands a packed W (n rows of k/2
+ * bytes) once into n rows of k bytes in the byte order the GEMM's tensor-core stage consumes
+ * (w_expanded_d: n * k bytes, 16-byte aligned); int4_linear_launch_prepared_async then runs the
+ * operator with that buffer in place of the packed weights, so that only the activations go
+ * through the in-kernel unpack.  Same results bit for bit; costs twice the weight memory and is
+ * meant for compute-bound shapes (decode shapes should keep the packed form: they are bound by
+ * weight bytes).  bias_d as in int4_linear_bias_launch_async (NULL = none).  No reference
+ * counterpart: the reference has one weight format.
+ */
+int int4_linear_prepare_weights(const void* w_packed_d, void* w_expanded_d, int n, int k, void* stream);
+int int4_linear_launch_prepared_async(const void* x_packed_d, const void* w_expanded_d, const int* bias_d,
+                                      void* y_d, int m, int n, int k, void* stream);
+
+/*
  * Host-buffer form of the call sequence in test/test_correctness.cu:53-63
  * (cudaMalloc x3, cudaMemcpy H2D x2, launch, cudaMemcpy D2H): operands and
  * result live in host memory; the library stages them through device buffers
@@ -132,6 +146,18 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
  * Returns the previous mode, or -INT4L_ERR_INVALID_ARG.  Environment: INT4L_OVERLAP.
  * No reference counterpart (the reference launcher synchronises the device after every call). */
 int int4_linear_set_overlap(int mode);
+
+/* Two-pass execution (opt-in): a streaming pre-pass expands both packed operands to bytes in a
+ * scratch buffer the library keeps per device ((m + n) * k bytes, allocated with cudaMalloc on
+ * first need and grown when a larger shape arrives), then a GEMM kernel reads them with nothing
+ * but TMA and the tensor core on the shared-memory path.  Results are identical.  Measured on
+ * B200 it is within +-5 % of the fused kernel for the largest shapes and slower for smaller
+ * ones, so the dispatcher never picks it by itself.  mode: 1 = use it whenever the
+ * tensor-memory family runs; 0 or -1 = fused single-kernel path only (default; no scratch).
+ * Returns INT4L_OK, or INT4L_ERR_INVALID_ARG for any other mode (setting unchanged).
+ * Environment: INT4L_TWO_PASS.  Because the first use of a larger shape allocates, make that
+ * call before capturing a CUDA graph. */
+int int4_linear_set_two_pass(int mode);
 
 /* Which family the dispatcher would use for a shape (INT4L_PATH_*). */
 int int4_linear_path_for(int m, int n, int k);

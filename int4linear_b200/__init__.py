@@ -14,12 +14,15 @@ from .linear import (  # noqa: F401
     Int4LinearError,
     linear,
     linear_host,
+    linear_prepared,
+    prepare_weights,
     linear_v21_launch,
     last_status,
     launch_count,
     path_for,
     set_path,
     set_overlap,
+    set_two_pass,
     set_tuning,
     PATH_AUTO,
     PATH_TCGEN05,

@@ -13,6 +13,8 @@ SYMBOLS = {
     "int4_linear_launch": (None, [_VP, _VP, _VP, _I, _I, _I]),
     "int4_linear_launch_async": (_I, [_VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_bias_launch_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "int4_linear_prepare_weights": (_I, [_VP, _VP, _I, _I, _VP]),
+    "int4_linear_launch_prepared_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),
     "int4_linear_pack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_pack_i8": (_I, [_VP, _VP, _I, _I, _VP]),
@@ -22,6 +24,7 @@ SYMBOLS = {
     "int4_linear_set_path": (_I, [_I]),
     "int4_linear_set_tuning": (_I, [_I, _I, _I]),
     "int4_linear_set_overlap": (_I, [_I]),
+    "int4_linear_set_two_pass": (_I, [_I]),
     "int4_linear_path_for": (_I, [_I, _I, _I]),
     "int4_linear_device_info": (_I, [_I]),
     "int4_linear_launch_count": (_LL, []),

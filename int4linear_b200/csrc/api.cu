@@ -16,12 +16,14 @@ namespace {
 constexpr int kMaxDevices = 64;
 DeviceCtx g_ctx[kMaxDevices];
 bool g_ctx_ready[kMaxDevices];
-std::mutex g_mutex;
+std::mutex g_mutex;          // contexts and the host-buffer staging
+std::mutex g_scratch_mutex;  // two-pass scratch (taken inside dispatch, which may run under g_mutex)
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_path{-1};       // -1 = not yet read from the environment
 std::atomic<int> g_tile_n{0};      // 0 = automatic
 std::atomic<int> g_direct_store{-1};
 std::atomic<int> g_overlap{-1};    // -1 = not yet read from the environment
+std::atomic<int> g_two_pass{-2};   // -2 = not yet read from the environment
 std::atomic<int> g_pairs{-2};      // -2 = not yet read from the environment
 thread_local int t_last_status = INT4L_OK;
 
@@ -99,6 +101,18 @@ int stream_overlap_mode()
     return v;
 }
 
+int two_pass_mode()
+{
+    int v = g_two_pass.load();
+    if (v == -2) {
+        const char* e = std::getenv("INT4L_TWO_PASS");
+        v = e ? std::atoi(e) : -1;
+        if (v < -1 || v > 1) v = -1;
+        g_two_pass.store(v);
+    }
+    return v;
+}
+
 int forced_pairs()
 {
     int v = g_pairs.load();
@@ -150,6 +164,7 @@ DeviceCtx* current_ctx(int* status)
 
     int rc = setup_tcgen05(c);
     if (rc == INT4L_OK) rc = setup_tcgen05_ts(c);
+    if (rc == INT4L_OK) rc = setup_tcgen05_s8(c);
     if (rc == INT4L_OK) rc = setup_skinny(c);
     if (rc != INT4L_OK) { *status = rc; return nullptr; }
     c->attrs_set = true;
@@ -187,23 +202,6 @@ int choose_path(const DeviceCtx* ctx, const Problem& p)
     return INT4L_PATH_TCGEN05;
 }
 
-int dispatch(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
-{
-    switch (choose_path(ctx, p)) {
-        case INT4L_PATH_SKINNY: return launch_skinny(ctx, p, stream);
-        case INT4L_PATH_LEGACY: return launch_legacy(ctx, p, stream);
-        default: return launch_tcgen05(ctx, p, stream);
-    }
-}
-
-int poll_device_status(DeviceCtx* ctx)
-{
-    if (!ctx || !ctx->status_host) return INT4L_OK;
-    int s = *ctx->status_host;
-    if (s != INT4L_OK) *ctx->status_host = INT4L_OK;
-    return s;
-}
-
 int ensure_stage(void** buf, size_t* have, size_t need)
 {
     if (*have >= need) return INT4L_OK;
@@ -213,6 +211,54 @@ int ensure_stage(void** buf, size_t* have, size_t need)
     if (cudaMalloc(buf, need) != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
     *have = need;
     return INT4L_OK;
+}
+
+// Two-pass path: expand both operands into `scratch` ((m + n) * k bytes), then the byte GEMM.
+int run_two_pass(DeviceCtx* ctx, const Problem& p, void* scratch, cudaStream_t stream)
+{
+    uint8_t* xb = static_cast<uint8_t*>(scratch);
+    uint8_t* wb = xb + static_cast<size_t>(p.m) * p.k;
+    int rc = launch_expand(ctx, p.x, xb, p.m, p.w, wb, p.n, p.k, stream);
+    if (rc != INT4L_OK) return rc;
+    return launch_tcgen05_s8(ctx, p, xb, wb, stream);
+}
+
+// Whether the two-pass path pays for a shape: the pre-pass moves 1.5 * (m + n) * k bytes through
+// HBM, the GEMM it speeds up does 2 * m * n * k operations, so it needs both m and n large.
+bool two_pass_wanted(const Problem& p)
+{
+    // Measured on B200: within +-5 % of the fused kernel from 8192 x 8192 outputs upwards
+    // (K = 8192) and slower below, for 2.5x the operand traffic -- so it is never chosen
+    // automatically; callers opt in with int4_linear_set_two_pass(1).
+    (void)p;
+    return two_pass_mode() == 1;
+}
+
+int dispatch(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
+{
+    switch (choose_path(ctx, p)) {
+        case INT4L_PATH_SKINNY: return launch_skinny(ctx, p, stream);
+        case INT4L_PATH_LEGACY: return launch_legacy(ctx, p, stream);
+        default: break;
+    }
+    if (two_pass_wanted(p) && forced_pairs() < 0 && forced_tile_n() == 0) {
+        const size_t need = (static_cast<size_t>(p.m) + p.n) * p.k;
+        bool have;
+        {
+            std::lock_guard<std::mutex> lock(g_scratch_mutex);
+            have = ensure_stage(&ctx->scratch, &ctx->scratch_bytes, need) == INT4L_OK;
+        }
+        if (have) return run_two_pass(ctx, p, ctx->scratch, stream);
+    }
+    return launch_tcgen05(ctx, p, stream);
+}
+
+int poll_device_status(DeviceCtx* ctx)
+{
+    if (!ctx || !ctx->status_host) return INT4L_OK;
+    int s = *ctx->status_host;
+    if (s != INT4L_OK) *ctx->status_host = INT4L_OK;
+    return s;
 }
 
 }  // namespace
@@ -244,6 +290,30 @@ int int4_linear_bias_launch_async(const void* x, const void* w, const int* bias_
     if (!ctx) { t_last_status = rc; return rc; }
     Problem p{x, w, y, m, n, k, bias_d};
     rc = dispatch(ctx, p, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
+int int4_linear_prepare_weights(const void* w_packed_d, void* w_expanded_d, int n, int k, void* stream)
+{
+    int rc = check_args(w_packed_d, w_packed_d, w_expanded_d, 1, n, k);
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (ctx) rc = launch_expand_weights(ctx, w_packed_d, w_expanded_d, n, k, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
+int int4_linear_launch_prepared_async(const void* x, const void* w_expanded_d, const int* bias_d, void* y,
+                                      int m, int n, int k, void* stream)
+{
+    int rc = check_args(x, w_expanded_d, y, m, n, k);
+    if (rc == INT4L_OK && bias_d != nullptr && (reinterpret_cast<uintptr_t>(bias_d) & 3u)) rc = INT4L_ERR_MISALIGNED;
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{x, w_expanded_d, y, m, n, k, bias_d, true};
+    rc = launch_tcgen05(ctx, p, static_cast<cudaStream_t>(stream));
     t_last_status = rc;
     return rc;
 }
@@ -357,6 +427,13 @@ int int4_linear_set_path(int path)
     int prev = current_path();
     if (path >= INT4L_PATH_AUTO && path <= INT4L_PATH_SKINNY) g_path.store(path);
     return prev;
+}
+
+int int4_linear_set_two_pass(int mode)
+{
+    if (mode < -1 || mode > 1) return INT4L_ERR_INVALID_ARG;
+    g_two_pass.store(mode);
+    return INT4L_OK;
 }
 
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)

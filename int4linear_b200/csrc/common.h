@@ -21,6 +21,9 @@ struct Problem {
     // Optional int32 bias of length N added to every row of Y (nullptr = none).  Not part of the
     // reference operator (its README lists bias as future work); exact integer arithmetic.
     const int* bias = nullptr;
+    // True when `w` is not the packed matrix but its byte expansion made by
+    // int4_linear_prepare_weights (N x K bytes).
+    bool w_expanded = false;
 };
 
 // Per-device state created on the first call on that device.
@@ -40,6 +43,8 @@ struct DeviceCtx {
     void* stage_y = nullptr; size_t stage_y_bytes = 0;
     const void* stage_w_src = nullptr;  // host weights currently resident in stage_w
     size_t stage_w_src_bytes = 0;
+    // Scratch of the two-pass path (expanded operands), grown on demand.
+    void* scratch = nullptr; size_t scratch_bytes = 0;
     bool attrs_set = false;
 };
 
@@ -56,17 +61,24 @@ int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int e
 
 // Kernel launchers.  Each returns an INT4L_* status; none of them synchronises.
 int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+// GEMM on operands already expanded to bytes (second pass of the two-pass path).
+int launch_tcgen05_s8(DeviceCtx* ctx, const Problem& p, const void* x_bytes, const void* w_bytes, cudaStream_t stream);
 int launch_tcgen05_ts(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);  // X operand in tensor memory
 int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 int launch_legacy(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 
 // Device-side packer (packer.cu).  src_elem_bytes: 4 = int32 per element, 1 = int8.
 int launch_pack(DeviceCtx* ctx, const void* src, int src_elem_bytes, void* dst, int rows, int cols, cudaStream_t stream);
+// Expands one or two packed matrices (rows x k/2 bytes) to rows x k bytes in one launch.
+int launch_expand(DeviceCtx* ctx, const void* a_packed, void* a_bytes, int rows_a,
+                  const void* b_packed, void* b_bytes, int rows_b, int k, cudaStream_t stream);
+int launch_expand_weights(DeviceCtx* ctx, const void* w_packed, void* w_expanded, int n, int k, cudaStream_t stream);
 int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols, cudaStream_t stream);
 
 // One-off function attribute set-up (dynamic shared memory opt-in).
 int setup_tcgen05(DeviceCtx* ctx);
 int setup_tcgen05_ts(DeviceCtx* ctx);
+int setup_tcgen05_s8(DeviceCtx* ctx);
 int setup_skinny(DeviceCtx* ctx);
 
 // Launch counter (kernels of this library launched by this process).
@@ -80,6 +92,7 @@ bool skinny_supports(const DeviceCtx* ctx, const Problem& p);
 bool getenv_flag_direct_store();
 int forced_tile_n();
 int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
+int two_pass_mode();  // -1 automatic, 0 never, 1 whenever the tensor-memory family is used
 int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 pairs with both operands in smem, 2 pairs with X in TMEM
 
 }  // namespace i4l

@@ -42,6 +42,7 @@
 //   |256 * y| <= 256 * 64 * K < 2^31 needs K < 131072.
 #include "common.h"
 #include "ptx.cuh"
+#include "epilogue.cuh"
 
 #define I4L_TRACE_EXPORT int4_linear_debug_trace
 #include "trace.cuh"
@@ -58,18 +59,22 @@ constexpr int kUnpackWarps = kGroups * kWarpsPerGroup;
 constexpr int kThreads = 32 * (2 + 4 + kUnpackWarps);
 constexpr int kStoreStageBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
 
-template <int BN, int P, int U, int CTAS>
+// PREW: the W operand arrives already expanded to bytes (int4_linear_prepare_weights), so
+// TMA drops its tile straight into the expanded ring and only X goes through the unpack.
+template <int BN, int P, int U, int CTAS, bool PREW = false>
 struct Cfg {
+    static constexpr bool kPreW = PREW;
     static constexpr int kBN = BN;
     static constexpr int kP = P;
     static constexpr int kU = U;
     static constexpr int kCtas = CTAS;
     static constexpr int kTileM = kBM * CTAS;                    // rows of the (cluster) tile
     static constexpr int kRowsW = BN / CTAS;                     // W rows this CTA loads and unpacks
-    static constexpr int kPkStage = (kBM + kRowsW) * kBKBytes;     // packed X then packed W
+    static constexpr int kPkRows = kBM + (PREW ? 0 : kRowsW);      // rows that go through the unpack
+    static constexpr int kPkStage = kPkRows * kBKBytes;            // packed X then (unless PREW) packed W
     static constexpr int kUpStage = (kBM + kRowsW) * 2 * kBKBytes; // s8 X (16 KB) then s8 W
     static constexpr int kTmemCols = 2 * BN;                     // two accumulator buffers
-    static constexpr int kNumBarriers = 2 * P + 2 * U + 4;
+    static constexpr int kNumBarriers = 2 * P + 2 * U + 4 + U;     // the last U: "expanded W has landed" (PREW)
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + U * kUpStage + P * kPkStage +
                                       kStoreStageBytes + kNumBarriers * 8 + 16;
     static_assert(P >= kGroups && U >= kGroups, "every unpack group needs a slot of its own");
@@ -101,6 +106,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
     auto up_empty = [&](int i) { return bar_base + 8u * (2 * P + U + i); };
     auto tm_full  = [&](int i) { return bar_base + 8u * (2 * P + 2 * U + i); };
     auto tm_empty = [&](int i) { return bar_base + 8u * (2 * P + 2 * U + 2 + i); };
+    auto w_full   = [&](int i) { return bar_base + 8u * (2 * P + 2 * U + 4 + i); };
     const uint32_t misc_off = (bar_base - base) + 8u * C::kNumBarriers;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + misc_off + 4);
@@ -118,6 +124,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         // up_full and tm_empty of CTA 0 collect the arrivals of both CTAs of a pair.
         for (int i = 0; i < U; ++i) { mbar_init(up_full(i), kWarpsPerGroup * CTAS); mbar_init(up_empty(i), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(tm_full(i), 1); mbar_init(tm_empty(i), 4 * CTAS); }
+        for (int i = 0; i < U; ++i) mbar_init(w_full(i), 1);
         *abort_flag = 0;
         mbar_init_fence();
         tma_prefetch_desc(&tm_x);
@@ -162,8 +169,18 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                     mbar_expect_tx(pk_full(s), C::kPkStage);
                     const uint32_t dst = pk_base + s * C::kPkStage;
                     tma_load_2d(dst, &tm_x, pk_full(s), kb * kBKBytes, (tm * CTAS + cta_rank) * kBM);
-                    tma_load_2d(dst + kBM * kBKBytes, &tm_w, pk_full(s), kb * kBKBytes,
-                                tn * BN + cta_rank * C::kRowsW);
+                    if constexpr (!C::kPreW) {
+                        tma_load_2d(dst + kBM * kBKBytes, &tm_w, pk_full(s), kb * kBKBytes,
+                                    tn * BN + cta_rank * C::kRowsW);
+                    } else {
+                        // Expanded W goes directly into the slot the UMMA reads; that slot is free
+                        // once the UMMAs of its previous use have been committed.
+                        const uint32_t us = it % U, ur = it / U;
+                        if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                        mbar_expect_tx(w_full(us), C::kRowsW * 128);
+                        tma_load_2d(up_base + us * C::kUpStage + kBM * 128, &tm_w, w_full(us), kb * 128,
+                                    tn * BN + cta_rank * C::kRowsW);
+                    }
                 }
             }
         }
@@ -206,7 +223,6 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         // ---------------------------------------------------------- epilogue
         const int sp = warp & 3;  // TMEM sub-partition this warp may read
         const uint32_t stage0 = st_base + (warp - 2) * 8192;
-        const bool vec_ok = (n & 3) == 0;
         uint32_t local_tile = 0;
         uint32_t chunk_no = 0;
         bool alive = true;
@@ -219,58 +235,9 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 1);
             tc_fence_after_sync();
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
-            const int row = row0 + lane;
             const int col0 = tn * BN;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                // A chunk entirely outside Y is skipped as a whole, so that the staging buffers
-                // alternate exactly with the store groups that were committed.
-                if (kTmaStore && !(row0 < m && col0 + c < n)) continue;
-                uint32_t v[32];
-                tmem_ld_32x32(t_addr + c, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = static_cast<uint32_t>(static_cast<int>(v[i]) >> 8);
-                if (bias != nullptr) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col0 + c + i < n) v[i] += static_cast<uint32_t>(__ldg(bias + col0 + c + i));
-                }
-                if constexpr (kTmaStore) {
-                    const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
-                    // The store issued two chunks ago read this buffer; make sure it is done.
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-#pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        sts128(stg + lane * 128 + ((q ^ (lane & 7)) << 4),
-                               make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tm_y, stg, col0 + c, row0);
-                        tma_store_commit();
-                    }
-                    ++chunk_no;
-                } else {
-                    if (row < m) {
-                        int* dst = y + static_cast<size_t>(row) * n + col0 + c;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const int col = col0 + c + 4 * q;
-                            if (vec_ok && col + 3 < n) {
-                                *reinterpret_cast<int4*>(dst + 4 * q) =
-                                    make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (col + e < n) dst[4 * q + e] = static_cast<int>(v[4 * q + e]);
-                            }
-                        }
-                    }
-                }
-            }
+            drain_accumulator<BN, kTmaStore>(t_addr, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -290,7 +257,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         const int group = uw / kWarpsPerGroup;
         const int gtid = (uw % kWarpsPerGroup) * 32 + lane;
         constexpr int kGroupThreads = kWarpsPerGroup * 32;
-        constexpr int kChunks = (kBM + C::kRowsW) * 4;  // 16-byte packed chunks per stage
+        constexpr int kChunks = C::kPkRows * 4;  // 16-byte packed chunks per stage
         constexpr int kPerThread = kChunks / kGroupThreads;
         static_assert(kChunks % kGroupThreads == 0, "unpack loop must divide evenly");
         uint32_t it = 0;
@@ -328,6 +295,10 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                 if (gtid == 0) I4L_TRACE_PUT(4, it, 0);
                 fence_proxy_async_smem();
                 if (gtid == 0) I4L_TRACE_PUT(4, it, 1);
+                if constexpr (C::kPreW) {
+                    // The slot is complete only when TMA has also delivered its expanded W rows.
+                    if (!mbar_wait(w_full(us), ur & 1u, abort_flag)) { alive = false; break; }
+                }
                 __syncwarp();
                 if (gtid == 0) I4L_TRACE_PUT(4, it, 2);
                 if (lane == 0) {
@@ -363,6 +334,8 @@ using Cfg256 = Cfg<256, 3, 2, 1>;
 using Cfg128 = Cfg<128, 4, 3, 1>;
 using Cfg64 = Cfg<64, 4, 4, 1>;
 using Cfg256x2 = Cfg<256, 4, 3, 2>;  // 256 x 256 tile on a CTA pair
+using Cfg256x2W = Cfg<256, 4, 4, 2, true>;  // the same with pre-expanded weights
+using Cfg128W = Cfg<128, 4, 4, 1, true>;
 
 template <class C, bool kTmaStore>
 int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
@@ -373,7 +346,10 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     CUtensorMap tm_x, tm_w, tm_y;
     int rc = make_tensor_map_2d(ctx, &tm_x, p.x, 1, pitch, p.m, pitch, kBKBytes, kBM, false);
     if (rc != INT4L_OK) return rc;
-    rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW, false);
+    if (C::kPreW)  // expanded weights: K bytes per row, 128-byte swizzled boxes
+        rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, static_cast<uint64_t>(p.k), p.n, static_cast<uint64_t>(p.k), 128, C::kRowsW, true);
+    else
+        rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW, false);
     if (rc != INT4L_OK) return rc;
     if (kTmaStore) {
         rc = make_tensor_map_2d(ctx, &tm_y, p.y, 4, p.n, p.m, static_cast<uint64_t>(p.n) * 4, 32, 32, true);
@@ -421,6 +397,8 @@ int setup_tcgen05(DeviceCtx* ctx)
     if (rc == INT4L_OK) rc = set_attr<Cfg128>();
     if (rc == INT4L_OK) rc = set_attr<Cfg64>();
     if (rc == INT4L_OK) rc = set_attr<Cfg256x2>();
+    if (rc == INT4L_OK) rc = set_attr<Cfg256x2W>();
+    if (rc == INT4L_OK) rc = set_attr<Cfg128W>();
     if (rc != INT4L_OK) return rc;
     // How many CTA pairs the device can hold at once (pairs must sit in one GPC-level
     // neighbourhood, so this can be below sm_count / 2).
@@ -450,6 +428,12 @@ int setup_tcgen05(DeviceCtx* ctx)
 int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
     const bool tma_store = (p.n % 4 == 0) && !getenv_flag_direct_store();
+    if (p.w_expanded) {
+        // Pre-expanded weights: CTA pairs whenever there is more than one row block, else one CTA.
+        if (p.m > 128)
+            return tma_store ? launch_cfg<Cfg256x2W, true>(ctx, p, stream) : launch_cfg<Cfg256x2W, false>(ctx, p, stream);
+        return tma_store ? launch_cfg<Cfg128W, true>(ctx, p, stream) : launch_cfg<Cfg128W, false>(ctx, p, stream);
+    }
     const long long tiles_m = (p.m + kBM - 1) / kBM;
     auto tiles = [&](int bn) { return tiles_m * ((p.n + bn - 1) / bn); };
     int bn = 256;

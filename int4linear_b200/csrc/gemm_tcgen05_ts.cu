@@ -24,6 +24,7 @@
 // reads conflict-free.
 #include "common.h"
 #include "ptx.cuh"
+#include "epilogue.cuh"
 
 #define I4L_TRACE_EXPORT int4_linear_debug_trace_ts
 #include "trace.cuh"
@@ -170,7 +171,6 @@ gemm_s4_tcgen05_ts_kernel(const __grid_constant__ CUtensorMap tm_x,
         // ---------------------------------------------------------- epilogue
         const int sp = warp & 3;
         const uint32_t stage0 = st_base + (warp - 2) * 8192;
-        const bool vec_ok = (n & 3) == 0;
         uint32_t local_tile = 0, chunk_no = 0;
         bool alive = true;
         for (int tile = worker; alive && tile < num_tiles; tile += workers, ++local_tile) {
@@ -180,57 +180,9 @@ gemm_s4_tcgen05_ts_kernel(const __grid_constant__ CUtensorMap tm_x,
             if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
             const int row0 = (tm * 2 + static_cast<int>(cta_rank)) * kBM + sp * 32;
-            const int row = row0 + lane;
             const int col0 = tn * kBN;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * kBN;
-#pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                // A chunk entirely outside Y is skipped as a whole, so that the staging buffers
-                // alternate exactly with the store groups that were committed.
-                if (kTmaStore && !(row0 < m && col0 + c < n)) continue;
-                uint32_t v[32];
-                tmem_ld_32x32(t_addr + c, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = static_cast<uint32_t>(static_cast<int>(v[i]) >> 8);
-                if (bias != nullptr) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col0 + c + i < n) v[i] += static_cast<uint32_t>(__ldg(bias + col0 + c + i));
-                }
-                if constexpr (kTmaStore) {
-                    const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
-                    if (lane == 0) tma_store_wait_read<1>();
-                    __syncwarp();
-#pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        sts128(stg + lane * 128 + ((q ^ (lane & 7)) << 4),
-                               make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        tma_store_2d(&tm_y, stg, col0 + c, row0);
-                        tma_store_commit();
-                    }
-                    ++chunk_no;
-                } else {
-                    if (row < m) {
-                        int* dst = y + static_cast<size_t>(row) * n + col0 + c;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const int col = col0 + c + 4 * q;
-                            if (vec_ok && col + 3 < n) {
-                                *reinterpret_cast<int4*>(dst + 4 * q) =
-                                    make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (col + e < n) dst[4 * q + e] = static_cast<int>(v[4 * q + e]);
-                            }
-                        }
-                    }
-                }
-            }
+            drain_accumulator<kBN, kTmaStore>(t_addr, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tm_empty(buf), 0);

@@ -76,6 +76,47 @@ unpack_s4_kernel(const uint32_t* __restrict__ src, int* __restrict__ dst, int ro
     }
 }
 
+// Operand expansion (first pass of the two-pass path, and int4_linear_prepare_weights): each
+// 16-byte packed chunk (32 elements) becomes 32 bytes -- the 16 even elements, then the 16 odd
+// ones, every byte equal to 16 x element -- which is byte for byte what the fused GEMM's unpack
+// warps write for that chunk.  HBM-bound: reads rows*K/2 bytes, writes rows*K.  One launch can
+// expand two matrices (X and W); chunks [0, chunks_a) belong to the first.
+__device__ __forceinline__ void expand_chunk(const uint4 x, uint4& lo, uint4& hi)
+{
+    lo.x = (x.x << 4) & 0xF0F0F0F0u; hi.x = x.x & 0xF0F0F0F0u;
+    lo.y = (x.y << 4) & 0xF0F0F0F0u; hi.y = x.y & 0xF0F0F0F0u;
+    lo.z = (x.z << 4) & 0xF0F0F0F0u; hi.z = x.z & 0xF0F0F0F0u;
+    lo.w = (x.w << 4) & 0xF0F0F0F0u; hi.w = x.w & 0xF0F0F0F0u;
+}
+
+__global__ void __launch_bounds__(kPackThreads)
+expand_kernel(const uint4* __restrict__ src_a, uint4* __restrict__ dst_a, long long chunks_a,
+              const uint4* __restrict__ src_b, uint4* __restrict__ dst_b, long long chunks_b)
+{
+    constexpr int kUnroll = 4;  // independent 16-byte loads in flight per thread
+    const long long total = chunks_a + chunks_b;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
+        uint4 x[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < total) x[u] = i < chunks_a ? __ldg(src_a + i) : __ldg(src_b + (i - chunks_a));
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < total) {
+                uint4 lo, hi;
+                expand_chunk(x[u], lo, hi);
+                uint4* d = i < chunks_a ? dst_a + 2 * i : dst_b + 2 * (i - chunks_a);
+                d[0] = lo;
+                d[1] = hi;
+            }
+        }
+    }
+}
+
 int grid_for(const DeviceCtx* ctx, long long words)
 {
     long long blocks = (words + kPackThreads - 1) / kPackThreads;
@@ -95,6 +136,28 @@ int launch_pack(DeviceCtx* ctx, const void* src, int src_elem_bytes, void* dst, 
         pack_s4_kernel<signed char><<<grid_for(ctx, words), kPackThreads, 0, stream>>>(static_cast<const signed char*>(src), static_cast<uint32_t*>(dst), rows, cols, wpr);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+int launch_expand(DeviceCtx* ctx, const void* a_packed, void* a_bytes, int rows_a,
+                  const void* b_packed, void* b_bytes, int rows_b, int k, cudaStream_t stream)
+{
+    const long long chunks_a = static_cast<long long>(rows_a) * (k / 32);  // k % 32 == 0
+    const long long chunks_b = static_cast<long long>(rows_b) * (k / 32);
+    const long long per_block = static_cast<long long>(kPackThreads) * 4;
+    long long blocks = (chunks_a + chunks_b + per_block - 1) / per_block;
+    const long long cap = static_cast<long long>(ctx->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    expand_kernel<<<static_cast<int>(blocks), kPackThreads, 0, stream>>>(
+        static_cast<const uint4*>(a_packed), static_cast<uint4*>(a_bytes), chunks_a,
+        static_cast<const uint4*>(b_packed), static_cast<uint4*>(b_bytes), chunks_b);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+int launch_expand_weights(DeviceCtx* ctx, const void* w_packed, void* w_expanded, int n, int k, cudaStream_t stream)
+{
+    return launch_expand(ctx, w_packed, w_expanded, n, nullptr, nullptr, 0, k, stream);
 }
 
 int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols, cudaStream_t stream)

@@ -120,6 +120,42 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias
     return out
 
 
+def prepare_weights(w_packed, k: int | None = None, stream=None):
+    """Expand packed CUDA weights [n, k/2] once into the [n, k] uint8 layout that
+    linear_prepared consumes (see int4_linear_prepare_weights)."""
+    import torch
+    wb = w_packed.contiguous().view(torch.uint8)
+    n = wb.shape[0]
+    k = k or wb.shape[1] * 2
+    out = torch.empty((n, k), dtype=torch.uint8, device=wb.device)
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    with torch.cuda.device(wb.device):
+        st = _lib.load().int4_linear_prepare_weights(wb.data_ptr(), out.data_ptr(), n, k, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_prepare_weights")
+    return out
+
+
+def linear_prepared(x_packed, w_expanded, out=None, bias=None, stream=None):
+    """Y = X @ W^T (+ bias) with weights from prepare_weights (asynchronous)."""
+    import torch
+    xb = x_packed.contiguous().view(torch.uint8)
+    m, k = xb.shape[0], xb.shape[1] * 2
+    n = w_expanded.shape[0]
+    if w_expanded.shape[1] != k or w_expanded.dtype != torch.uint8 or not w_expanded.is_contiguous():
+        raise ValueError("w_expanded must be the contiguous [n, k] uint8 tensor made by prepare_weights")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.int32, device=xb.device)
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    with torch.cuda.device(xb.device):
+        st = _lib.load().int4_linear_launch_prepared_async(
+            xb.data_ptr(), w_expanded.data_ptr(), bias.data_ptr() if bias is not None else None,
+            out.data_ptr(), m, n, k, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_launch_prepared_async")
+    return out
+
+
 def linear_host(x_packed: np.ndarray, w_packed: np.ndarray, k: int, out: np.ndarray | None = None,
                 w_resident: bool = False) -> np.ndarray:
     """The whole host-side sequence of the reference's correctness program
@@ -155,6 +191,14 @@ def set_tuning(tile_n: int = 0, direct_store: bool = False, cta_pairs: int = -1)
     st = _lib.load().int4_linear_set_tuning(tile_n, 1 if direct_store else 0, cta_pairs)
     if st != 0:
         raise Int4LinearError(st, "int4_linear_set_tuning")
+
+
+def set_two_pass(mode: int) -> int:
+    """-1 automatic, 0 never, 1 always for the tensor-memory family (int4_linear_set_two_pass)."""
+    st = _lib.load().int4_linear_set_two_pass(mode)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_set_two_pass")
+    return st
 
 
 def set_overlap(mode: int) -> int:

@@ -9,7 +9,7 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False, pairs=-1):
+def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False, pairs=-1, two_pass=0):
     """Upload packed operands, run one blocking launch through the C ABI, download Y."""
     import torch
     xd = torch.from_numpy(xp).to(cuda)
@@ -18,11 +18,13 @@ def run_device(cuda, xp, wp, k, path=L.PATH_AUTO, tile_n=0, direct=False, pairs=
     yd = torch.full((m, n), -12345, dtype=torch.int32, device=cuda)
     prev = L.set_path(path)
     L.set_tuning(tile_n, direct, pairs)
+    L.set_two_pass(two_pass)
     try:
         L.linear_v21_launch(xd, wd, yd, m, n, k)
     finally:
         L.set_path(prev)
         L.set_tuning(0, False, -1)
+        L.set_two_pass(-1)
     return yd.cpu().numpy()
 
 
@@ -35,6 +37,8 @@ VARIANTS = [
     ("tcgen05-pairs-direct", dict(path=L.PATH_TCGEN05, pairs=1, direct=True)),
     ("tcgen05-pairs-xtmem-tma", dict(path=L.PATH_TCGEN05, pairs=2)),
     ("tcgen05-pairs-xtmem-direct", dict(path=L.PATH_TCGEN05, pairs=2, direct=True)),
+    ("two-pass-tma", dict(path=L.PATH_TCGEN05, two_pass=1)),
+    ("two-pass-direct", dict(path=L.PATH_TCGEN05, two_pass=1, direct=True)),
     ("legacy", dict(path=L.PATH_LEGACY)),
     ("auto", dict(path=L.PATH_AUTO)),
 ]
@@ -140,6 +144,19 @@ def test_host_buffer_entry_point(cuda):
     assert L.launch_count() == before + 2
 
 
+def test_host_buffer_entry_point_with_two_pass(cuda):
+    """The host-buffer entry point must work when the dispatcher takes the two-pass path (it keeps
+    its own staging lock while the two-pass scratch is looked up)."""
+    m, n, k = 300, 264, 256
+    x, w, xp, wp = make_case(m, n, k, seed=8)
+    L.set_two_pass(1)
+    try:
+        y = L.linear_host(xp, wp, k)
+    finally:
+        L.set_two_pass(-1)
+    assert O.is_same(y, O.linear_ref(x.astype(np.int32), w.astype(np.int32)))
+
+
 def test_tensor_front_end(cuda):
     import torch
     m, n, k = 96, 160, 384
@@ -203,3 +220,32 @@ def test_fused_bias_is_exact(cuda, shape, variant):
     assert L.last_status() == 0
     want = O.linear_ref(x.astype(np.int32), w.astype(np.int32)) + bias[None, :]
     assert O.is_same(y.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 256), (128, 256, 128), (1024, 1024, 1024), (100, 77, 96), (513, 130, 1056), (16, 264, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("direct", [False, True], ids=["tma", "direct"])
+def test_prepared_weights_path(cuda, shape, direct):
+    """Weights expanded once by int4_linear_prepare_weights, then used in place of the packed ones."""
+    import torch
+    m, n, k = shape
+    x, w, xp, wp = make_case(m, n, k, seed=33)
+    wd = torch.from_numpy(wp).to(cuda)
+    we = L.prepare_weights(wd)
+    torch.cuda.synchronize()
+    # the expansion itself: 16 even elements then 16 odd ones of every 32, each times 16
+    w32 = w.reshape(n, k // 32, 32).astype(np.int16) * 16
+    want_bytes = np.concatenate([w32[:, :, 0::2], w32[:, :, 1::2]], axis=2).reshape(n, k).astype(np.int8)
+    assert np.array_equal(we.cpu().numpy().view(np.int8), want_bytes)
+    bias = (np.arange(n, dtype=np.int32) % 97) - 48
+    L.set_tuning(0, direct, -1)
+    try:
+        y = L.linear_prepared(torch.from_numpy(xp).to(cuda), we)
+        yb = L.linear_prepared(torch.from_numpy(xp).to(cuda), we, bias=torch.from_numpy(bias).to(cuda))
+        torch.cuda.synchronize()
+    finally:
+        L.set_tuning(0, False, -1)
+    assert L.last_status() == 0
+    ref = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+    assert O.is_same(y.cpu().numpy(), ref)
+    assert O.is_same(yb.cpu().numpy(), ref + bias[None, :])
