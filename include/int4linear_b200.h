@@ -91,6 +91,25 @@ int int4_linear_launch_prepared_async(const void* x_packed_d, const void* w_expa
                                       void* y_d, int m, int n, int k, void* stream);
 
 /*
+ * The two-pass operator (expand pre-pass + byte GEMM, see int4_linear_set_two_pass) for callers
+ * that are not allowed to allocate device memory: servers or frameworks that have handed the
+ * whole GPU to their own allocator, loops that cannot take the device-wide synchronisation of
+ * cudaMalloc/cudaFree, code under a no-allocation-after-start-up rule.  It has no counterpart
+ * in the reference.  Its scratch is a fixed 64 MiB array inside the library's device image --
+ * present on every GPU that loads the library, until the process exits -- so it accepts only
+ * (m + n) * k <= 67 108 864 and returns INT4L_ERR_TOO_LARGE beyond that.  It never calls
+ * cudaMalloc, cudaFree or any other allocating routine.  The first call on a device resolves the
+ * array's device address and sets kernel attributes; issue it before any stream capture on that
+ * device.  The array is shared by all calls and keeps the previous call's bytes (each call
+ * overwrites what it reads, nothing has to be cleared); calls that could overlap on one GPU race
+ * on it, so keep them ordered on one stream per device.  Same arguments and results as
+ * int4_linear_bias_launch_async; a device-side timeout of this entry point is not reported
+ * through int4_linear_last_status.
+ */
+int int4_linear_launch_static_scratch_async(const void* x_packed_d, const void* w_packed_d, const int* bias_d,
+                                            void* y_d, int m, int n, int k, void* stream);
+
+/*
  * Host-buffer form of the call sequence in test/test_correctness.cu:53-63
  * (cudaMalloc x3, cudaMemcpy H2D x2, launch, cudaMemcpy D2H): operands and
  * result live in host memory; the library stages them through device buffers
