@@ -261,6 +261,56 @@ int poll_device_status(DeviceCtx* ctx)
     return s;
 }
 
+// Large host-buffer problems are cut into up to eight row blocks of X / Y and run as a
+// three-stream pipeline -- upload of block i+1, GEMM of block i and download of block i-1 overlap --
+// because the download of Y (4 bytes per output) is by far the longest leg and PCIe is full duplex.
+int host_pipelined(DeviceCtx* ctx, const void* x_h, const void* w_h, void* y_h, int m, int n, int k, bool reuse_w)
+{
+    if (ctx->host_up == nullptr) {
+        bool ok = cudaStreamCreateWithFlags(&ctx->host_up, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&ctx->host_run, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaStreamCreateWithFlags(&ctx->host_down, cudaStreamNonBlocking) == cudaSuccess &&
+                  cudaEventCreateWithFlags(&ctx->host_ev_w, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < 8; ++i)
+            ok = cudaEventCreateWithFlags(&ctx->host_ev_x[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&ctx->host_ev_y[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) { cudaGetLastError(); ctx->host_up = nullptr; return INT4L_ERR_CUDA; }
+    }
+    const size_t row_x = static_cast<size_t>(k) / 2, row_y = static_cast<size_t>(n) * 4;
+    const int block = ((m + 7) / 8 + 255) / 256 * 256;  // rows per block, a multiple of the tile height
+    const uint8_t* xh = static_cast<const uint8_t*>(x_h);
+    uint8_t* yh = static_cast<uint8_t*>(y_h);
+    uint8_t* xd = static_cast<uint8_t*>(ctx->stage_x);
+    uint8_t* yd = static_cast<uint8_t*>(ctx->stage_y);
+    bool ok = true;
+    if (!reuse_w) {
+        ok = cudaMemcpyAsync(ctx->stage_w, w_h, static_cast<size_t>(n) * row_x, cudaMemcpyHostToDevice, ctx->host_up) == cudaSuccess &&
+             cudaEventRecord(ctx->host_ev_w, ctx->host_up) == cudaSuccess &&
+             cudaStreamWaitEvent(ctx->host_run, ctx->host_ev_w, 0) == cudaSuccess;
+    }
+    int rc = INT4L_OK;
+    for (int i = 0, r0 = 0; ok && r0 < m; ++i, r0 += block) {
+        const int rows = m - r0 < block ? m - r0 : block;
+        ok = cudaMemcpyAsync(xd + r0 * row_x, xh + r0 * row_x, rows * row_x, cudaMemcpyHostToDevice, ctx->host_up) == cudaSuccess &&
+             cudaEventRecord(ctx->host_ev_x[i], ctx->host_up) == cudaSuccess &&
+             cudaStreamWaitEvent(ctx->host_run, ctx->host_ev_x[i], 0) == cudaSuccess;
+        if (!ok) break;
+        Problem p{xd + r0 * row_x, ctx->stage_w, yd + r0 * row_y, rows, n, k};
+        rc = dispatch(ctx, p, ctx->host_run);
+        if (rc != INT4L_OK) break;
+        ok = cudaEventRecord(ctx->host_ev_y[i], ctx->host_run) == cudaSuccess &&
+             cudaStreamWaitEvent(ctx->host_down, ctx->host_ev_y[i], 0) == cudaSuccess &&
+             cudaMemcpyAsync(yh + r0 * row_y, yd + r0 * row_y, rows * row_y, cudaMemcpyDeviceToHost, ctx->host_down) == cudaSuccess;
+    }
+    // Drain all three streams whatever happened, so that no copy is left in flight on return.
+    const bool drained = cudaStreamSynchronize(ctx->host_up) == cudaSuccess &&
+                         cudaStreamSynchronize(ctx->host_run) == cudaSuccess &&
+                         cudaStreamSynchronize(ctx->host_down) == cudaSuccess;
+    if (rc != INT4L_OK) return rc;
+    if (!ok || !drained) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+    return INT4L_OK;
+}
+
 }  // namespace
 
 }  // namespace i4l
@@ -346,19 +396,25 @@ int int4_linear_host(const void* x_h, const void* w_h, void* y_h, int m, int n, 
         if (rc == INT4L_OK) rc = ensure_stage(&ctx->stage_y, &ctx->stage_y_bytes, yb);
         if (rc != INT4L_OK) { t_last_status = rc; return rc; }
         const bool reuse = w_resident && !w_buf_grew && ctx->stage_w_src == w_h && ctx->stage_w_src_bytes == wb;
-        cudaError_t e = cudaMemcpyAsync(ctx->stage_x, x_h, xb, cudaMemcpyHostToDevice, nullptr);
-        if (e == cudaSuccess && !reuse) {
-            e = cudaMemcpyAsync(ctx->stage_w, w_h, wb, cudaMemcpyHostToDevice, nullptr);
-            ctx->stage_w_src = w_h;
-            ctx->stage_w_src_bytes = wb;
+        if (m >= 1024 && yb >= (16u << 20)) {
+            rc = host_pipelined(ctx, x_h, w_h, y_h, m, n, k, reuse);
+            if (!reuse) { ctx->stage_w_src = w_h; ctx->stage_w_src_bytes = wb; }
+            if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+        } else {
+            cudaError_t e = cudaMemcpyAsync(ctx->stage_x, x_h, xb, cudaMemcpyHostToDevice, nullptr);
+            if (e == cudaSuccess && !reuse) {
+                e = cudaMemcpyAsync(ctx->stage_w, w_h, wb, cudaMemcpyHostToDevice, nullptr);
+                ctx->stage_w_src = w_h;
+                ctx->stage_w_src_bytes = wb;
+            }
+            if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
+            Problem p{ctx->stage_x, ctx->stage_w, ctx->stage_y, m, n, k};
+            rc = dispatch(ctx, p, nullptr);
+            if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+            e = cudaMemcpyAsync(y_h, ctx->stage_y, yb, cudaMemcpyDeviceToHost, nullptr);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+            if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
         }
-        if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
-        Problem p{ctx->stage_x, ctx->stage_w, ctx->stage_y, m, n, k};
-        rc = dispatch(ctx, p, nullptr);
-        if (rc != INT4L_OK) { t_last_status = rc; return rc; }
-        e = cudaMemcpyAsync(y_h, ctx->stage_y, yb, cudaMemcpyDeviceToHost, nullptr);
-        if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
-        if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
     }
     rc = poll_device_status(ctx);
     t_last_status = rc;

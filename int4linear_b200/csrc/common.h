@@ -41,6 +41,9 @@ struct DeviceCtx {
     void* stage_x = nullptr; size_t stage_x_bytes = 0;
     void* stage_w = nullptr; size_t stage_w_bytes = 0;
     void* stage_y = nullptr; size_t stage_y_bytes = 0;
+    // Streams and events of the pipelined host-buffer path (created on first use).
+    cudaStream_t host_up = nullptr, host_run = nullptr, host_down = nullptr;
+    cudaEvent_t host_ev_w = nullptr, host_ev_x[8] = {}, host_ev_y[8] = {};
     const void* stage_w_src = nullptr;  // host weights currently resident in stage_w
     size_t stage_w_src_bytes = 0;
     // Scratch of the two-pass path (expanded operands), grown on demand.

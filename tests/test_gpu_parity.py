@@ -144,6 +144,19 @@ def test_host_buffer_entry_point(cuda):
     assert L.launch_count() == before + 2
 
 
+def test_host_buffer_entry_point_pipelined(cuda):
+    """Large host-buffer calls run as row blocks on three streams (upload / GEMM / download); the
+    last block here is ragged and the weights are declared resident on the second call."""
+    m, n, k = 2148, 2048, 256
+    x, w, xp, wp = make_case(m, n, k, seed=14)
+    y = L.linear_host(xp, wp, k)
+    assert O.is_same(y, O.linear_ref_sgemm(x, w))
+    x2 = L.uniform_s4(78, m, k)
+    y2 = L.linear_host(L.pack_bytes(x2), wp, k, w_resident=True)
+    assert O.is_same(y2, O.linear_ref_sgemm(x2, w))
+    assert L.last_status() == 0
+
+
 def test_host_buffer_entry_point_with_two_pass(cuda):
     """The host-buffer entry point must work when the dispatcher takes the two-pass path (it keeps
     its own staging lock while the two-pass scratch is looked up)."""
