@@ -15,11 +15,11 @@
 //   the W work per CTA matters because shared-memory bandwidth, not the tensor
 //   pipe, is what limits this kernel.  K advances in blocks of 128 elements
 //   (64 packed bytes per row).
-//   Warp roles (704 threads):
+//   Warp roles (448 threads):
 //     warp 0      TMA producer: packed X tile (128 x 64 B) and W tile (BN x 64 B)
 //                 per K block into the "packed" ring; OOB rows/bytes read as 0,
 //                 which implements every M, N and K tail.
-//     warps 6-21  unpack, as two groups of eight warps that take alternate K
+//     warps 6-13  unpack, as two groups of four warps that take alternate K
 //                 blocks: read the packed ring, expand nibbles to bytes, write the
 //                 "unpacked" ring in the UMMA K-major 128-byte-swizzled layout,
 //                 release the packed slot.
@@ -54,7 +54,7 @@ namespace {
 constexpr int kBM = 128;          // tile rows (UMMA M)
 constexpr int kBKBytes = 64;      // packed bytes per row per K block (128 elements)
 constexpr int kGroups = 2;         // unpack groups, each converting every kGroups-th K block
-constexpr int kWarpsPerGroup = 8;
+constexpr int kWarpsPerGroup = 4;   // measured: 8 unpack warps in all are enough, 16 only add contention
 constexpr int kUnpackWarps = kGroups * kWarpsPerGroup;
 constexpr int kThreads = 32 * (2 + 4 + kUnpackWarps);
 constexpr int kStoreStageBytes = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
@@ -333,7 +333,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
 using Cfg256 = Cfg<256, 3, 2, 1>;
 using Cfg128 = Cfg<128, 4, 3, 1>;
 using Cfg64 = Cfg<64, 4, 4, 1>;
-using Cfg256x2 = Cfg<256, 4, 3, 2>;  // 256 x 256 tile on a CTA pair
+using Cfg256x2 = Cfg<256, 4, 4, 2>;  // 256 x 256 tile on a CTA pair (a fourth expanded slot is worth 4 %)
 using Cfg256x2W = Cfg<256, 4, 4, 2, true>;  // the same with pre-expanded weights
 using Cfg128W = Cfg<128, 4, 4, 1, true>;
 
