@@ -1,5 +1,5 @@
 // Shared epilogue of the tensor-memory GEMM kernels: one warp drains its 32 TMEM lanes
-// (32 output rows) x BN accumulator columns into Y.
+// (32 output rows) x `width` accumulator columns (a multiple of 32) into Y.
 //
 // The accumulator holds 256 * y (both operands were expanded to 16 x value), so each value is
 // shifted right by 8 (arithmetic, exact), the optional int32 bias of its column is added, and
@@ -15,8 +15,8 @@
 
 namespace i4l {
 
-template <int BN, bool kTmaStore>
-__device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int row0, int col0, int m, int n,
+template <bool kTmaStore>
+__device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, int row0, int col0, int m, int n,
                                                   int* __restrict__ y, const int* __restrict__ bias,
                                                   const CUtensorMap* tm_y, uint32_t stage0, uint32_t& chunk_no,
                                                   int lane)
@@ -24,7 +24,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int row0, int
     const int row = row0 + lane;
     const bool vec_ok = (n & 3) == 0;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
+    for (int c = 0; c < width; c += 32) {
         // A chunk entirely outside Y is skipped as a whole, so that the staging buffers
         // alternate exactly with the store groups that were committed.
         if (kTmaStore && !(row0 < m && col0 + c < n)) continue;
