@@ -77,6 +77,20 @@ int int4_linear_bias_launch_async(const void* x_packed_d, const void* w_packed_d
                                   void* y_d, int m, int n, int k, void* stream);
 
 /*
+ * The operator with a dequantising epilogue and bfloat16 output:
+ *     Y16[i][j] = bf16( float(sum_l X[i][l] * W[j][l]) * row_scale[i] * col_scale[j] + bias[j] )
+ * row_scale_d (m floats, per-token), col_scale_d (n floats, per-channel) and bias_d (n floats)
+ * are device pointers, each may be NULL (factor 1 / addend 0); y_bf16_d is m x n bfloat16,
+ * row-major, 16-byte aligned.  The integer sum is exact, its conversion to float is exact, the
+ * scaling is one float multiply and one fused multiply-add, the result is rounded to nearest
+ * even.  Halves the bytes of Y, the dominant stream of large shapes.  Always runs on the
+ * tensor-memory kernel family.  No reference counterpart (its output is int32 only).
+ */
+int int4_linear_scaled_launch_async(const void* x_packed_d, const void* w_packed_d, const float* row_scale_d,
+                                    const float* col_scale_d, const float* bias_d, void* y_bf16_d,
+                                    int m, int n, int k, void* stream);
+
+/*
  * Weight-stationary pre-layout.  int4_linear_prepare_weights expands a packed W (n rows of k/2
  * bytes) once into n rows of k bytes in the byte order the GEMM's tensor-core stage consumes
  * (w_expanded_d: n * k bytes, 16-byte aligned); int4_linear_launch_prepared_async then runs the

@@ -368,6 +368,23 @@ int int4_linear_launch_prepared_async(const void* x, const void* w_expanded_d, c
     return rc;
 }
 
+int int4_linear_scaled_launch_async(const void* x, const void* w, const float* row_scale_d, const float* col_scale_d,
+                                    const float* bias_d, void* y_bf16_d, int m, int n, int k, void* stream)
+{
+    int rc = check_args(x, w, y_bf16_d, m, n, k);
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{x, w, y_bf16_d, m, n, k};
+    p.scaled.row_scale = row_scale_d;
+    p.scaled.col_scale = col_scale_d;
+    p.scaled.bias = bias_d;
+    p.scaled.y16 = y_bf16_d;
+    rc = launch_tcgen05(ctx, p, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
 void int4_linear_launch(void* x, void* w, void* y, int m, int n, int k)
 {
     int rc = int4_linear_launch_async(x, w, y, m, n, k, nullptr);

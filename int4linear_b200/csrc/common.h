@@ -13,6 +13,16 @@ namespace i4l {
 // reference's (kernels/linear_v21.h:62-69): X is M x K and W is N x K, both
 // packed two signed nibbles per byte (low nibble = even index) with a row
 // pitch of K/2 bytes; Y is M x N int32, row-major.
+// Optional scaled bfloat16 output: Y16[i][j] = bf16(float(acc[i][j]) * row_scale[i] * col_scale[j] + bias[j]),
+// any of the three vectors may be null (factor 1 / addend 0).  Active when y16 is set; the int32 Y is
+// then not written.
+struct ScaledOut {
+    const float* row_scale = nullptr;  // m per-row (per-token) factors
+    const float* col_scale = nullptr;  // n per-column (per-channel) factors
+    const float* bias = nullptr;       // n addends
+    void* y16 = nullptr;               // m x n bfloat16, row-major
+};
+
 struct Problem {
     const void* x;
     const void* w;
@@ -24,6 +34,7 @@ struct Problem {
     // True when `w` is not the packed matrix but its byte expansion made by
     // int4_linear_prepare_weights (N x K bytes).
     bool w_expanded = false;
+    ScaledOut scaled;
 };
 
 // Per-device state created on the first call on that device.

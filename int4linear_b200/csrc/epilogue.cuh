@@ -11,6 +11,9 @@
 // Replaces the reference's per-thread int2 stores, kernels/linear_v21.h:661-710.
 #pragma once
 
+#include <cuda_bf16.h>
+
+#include "common.h"
 #include "ptx.cuh"
 
 namespace i4l {
@@ -69,6 +72,47 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
                             if (col + e < n) dst[4 * q + e] = static_cast<int>(v[4 * q + e]);
                     }
                 }
+            }
+        }
+    }
+}
+
+// Dequantising variant: float(acc) * row_scale[row] * col_scale[col] + bias[col], rounded to
+// bfloat16 (round to nearest even), written with per-thread 16-byte stores (8 values) where the
+// row pitch allows.  The int32 -> float conversion is exact (|acc| <= 64 K < 2^24).
+__device__ __forceinline__ void drain_accumulator_scaled(uint32_t t_addr, int width, int row0, int col0, int m, int n,
+                                                         const ScaledOut& so, int lane)
+{
+    const int row = row0 + lane;
+    const bool vec_ok = (n & 7) == 0;
+    const float rs = (so.row_scale != nullptr && row < m) ? __ldg(so.row_scale + row) : 1.0f;
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(so.y16);
+#pragma unroll 1
+    for (int c = 0; c < width; c += 32) {
+        if (col0 + c >= n) break;
+        uint32_t v[32];
+        tmem_ld_32x32(t_addr + c, v);
+        tmem_ld_wait();
+        if (row >= m) continue;
+        __align__(16) __nv_bfloat16 h[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int col = col0 + c + i;
+            const float cs = (so.col_scale != nullptr && col < n) ? __ldg(so.col_scale + col) : 1.0f;
+            const float b = (so.bias != nullptr && col < n) ? __ldg(so.bias + col) : 0.0f;
+            const float f = static_cast<float>(static_cast<int>(v[i]) >> 8);
+            h[i] = __float2bfloat16_rn(fmaf(f * rs, cs, b));
+        }
+        __nv_bfloat16* dst = out + static_cast<size_t>(row) * n + col0 + c;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int col = col0 + c + 8 * q;
+            if (vec_ok && col + 7 < n) {
+                *reinterpret_cast<uint4*>(dst + 8 * q) = *reinterpret_cast<const uint4*>(h + 8 * q);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (col + e < n) dst[8 * q + e] = h[8 * q + e];
             }
         }
     }

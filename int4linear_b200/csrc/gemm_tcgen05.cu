@@ -91,7 +91,8 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                        const __grid_constant__ CUtensorMap tm_wh,
                        const __grid_constant__ CUtensorMap tm_y,
                        int* __restrict__ y, int m, int n, int k,
-                       int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias)
+                       int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias,
+                       const ScaledOut so)
 {
     constexpr int BN = C::kBN, P = C::kP, U = C::kU, CTAS = C::kCtas;
     extern __shared__ uint8_t smem_raw[];
@@ -257,7 +258,10 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
-            drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
+            if (!kTmaStore && so.y16 != nullptr)
+                drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
+            else
+                drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -422,7 +426,7 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_kernel<C, kTmaStore>, tm_x, tm_w, tm_wh, tm_y,
                                        static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, split_from,
-                                       ctx->status_dev, p.bias);
+                                       ctx->status_dev, p.bias, p.scaled);
     count_launch();
     if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
     return INT4L_OK;
@@ -477,7 +481,7 @@ int setup_tcgen05(DeviceCtx* ctx)
 // machine leaves SMs idle.
 int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
-    const bool tma_store = (p.n % 4 == 0) && !getenv_flag_direct_store();
+    const bool tma_store = (p.n % 4 == 0) && !getenv_flag_direct_store() && p.scaled.y16 == nullptr;
     if (p.w_expanded) {
         // Pre-expanded weights: CTA pairs whenever there is more than one row block, else one CTA.
         if (p.m > 128)
@@ -497,7 +501,7 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     bool pairs = p.m > 128 && pair_tiles >= ctx->max_pairs;
     if (forced != 0) pairs = false;
     if (forced_pairs() >= 0) pairs = forced_pairs() != 0;
-    if (pairs && forced_pairs() == 2) return launch_tcgen05_ts(ctx, p, stream);
+    if (pairs && forced_pairs() == 2 && p.scaled.y16 == nullptr) return launch_tcgen05_ts(ctx, p, stream);
     if (pairs) return tma_store ? launch_cfg<Cfg256x2, true>(ctx, p, stream) : launch_cfg<Cfg256x2, false>(ctx, p, stream);
     if (bn == 256) return tma_store ? launch_cfg<Cfg256, true>(ctx, p, stream) : launch_cfg<Cfg256, false>(ctx, p, stream);
     if (bn == 128) return tma_store ? launch_cfg<Cfg128, true>(ctx, p, stream) : launch_cfg<Cfg128, false>(ctx, p, stream);

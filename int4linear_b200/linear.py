@@ -120,6 +120,30 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias
     return out
 
 
+def linear_scaled(x_packed, w_packed, row_scale=None, col_scale=None, bias=None, out=None, stream=None):
+    """bf16 Y = (X @ W^T) * row_scale[:, None] * col_scale[None, :] + bias (see
+    int4_linear_scaled_launch_async).  Scales and bias are CUDA float32 vectors or None."""
+    import torch
+    xb = x_packed.contiguous().view(torch.uint8)
+    wb = w_packed.contiguous().view(torch.uint8)
+    m, n, k = xb.shape[0], wb.shape[0], xb.shape[1] * 2
+    if wb.shape[1] * 2 != k:
+        raise ValueError("packed widths do not match")
+    for name, t, length in (("row_scale", row_scale, m), ("col_scale", col_scale, n), ("bias", bias, n)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != length or not t.is_cuda or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous CUDA float32 tensor with {length} elements")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=xb.device)
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    ptr = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+    with torch.cuda.device(xb.device):
+        st = _lib.load().int4_linear_scaled_launch_async(xb.data_ptr(), wb.data_ptr(), ptr(row_scale), ptr(col_scale),
+                                                         ptr(bias), out.data_ptr(), m, n, k, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_scaled_launch_async")
+    return out
+
+
 def prepare_weights(w_packed, k: int | None = None, stream=None):
     """Expand packed CUDA weights [n, k/2] once into the [n, k] uint8 layout that
     linear_prepared consumes (see int4_linear_prepare_weights)."""

@@ -262,3 +262,32 @@ def test_prepared_weights_path(cuda, shape, direct):
     ref = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
     assert O.is_same(y.cpu().numpy(), ref)
     assert O.is_same(yb.cpu().numpy(), ref + bias[None, :])
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 256), (1024, 1024, 512), (64, 72, 96), (257, 130, 1056), (4096, 4096, 1024)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_scaled_bf16_epilogue(cuda, shape):
+    """Dequantising epilogue: bf16(float(acc) * row_scale * col_scale + bias).  The integer part is
+    exact, so the only freedom is the float arithmetic (one multiply, one fused multiply-add) and
+    the final rounding to bfloat16: tolerance one bf16 unit in the last place (2^-7 relative)."""
+    import torch
+    m, n, k = shape
+    x, w, xp, wp = make_case(m, n, k, seed=51)
+    rng = np.random.default_rng(7)
+    rs = rng.uniform(0.01, 0.1, size=m).astype(np.float32)
+    cs = rng.uniform(0.005, 0.05, size=n).astype(np.float32)
+    b = rng.uniform(-1, 1, size=n).astype(np.float32)
+    xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+    acc = O.linear_ref_sgemm(x, w).astype(np.float32)
+    for use in [(True, True, True), (False, True, False), (False, False, False)]:
+        args = [torch.from_numpy(v).to(cuda) if u else None for v, u in zip((rs, cs, b), use)]
+        y = L.linear_scaled(xd, wd, *args)
+        torch.cuda.synchronize()
+        assert L.last_status() == 0
+        ref = acc * (rs[:, None] if use[0] else 1.0) * (cs[None, :] if use[1] else 1.0) + (b[None, :] if use[2] else 0.0)
+        got = y.float().cpu().numpy()
+        tol = np.abs(ref) * 2.0 ** -7 + 1e-6
+        assert np.all(np.abs(got - ref) <= tol), float(np.max(np.abs(got - ref) / (np.abs(ref) + 1e-6)))
+    # unscaled: bf16 of the exact integers (all |acc| here are exactly representable up to rounding)
+    exact = torch.from_numpy(acc).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(got, exact)
