@@ -40,7 +40,7 @@ extern "C" {
 #define INT4L_PATH_AUTO     0  /* shape dispatch (default)                                   */
 #define INT4L_PATH_TCGEN05  1  /* TMA -> s4->s8 unpack -> tcgen05.mma kind::i8 -> TMEM        */
 #define INT4L_PATH_LEGACY   2  /* warp-level mma.sync m16n8k64 s4 (pre-Blackwell instruction) */
-#define INT4L_PATH_SKINNY   3  /* register-streaming kernel for m <= 64 (decode shapes)      */
+#define INT4L_PATH_SKINNY   3  /* register-streaming kernels, m <= 64 (chosen for m <= 32)    */
 
 /*
  * Drop-in for `void linear_v21_launch(void*, void*, void*, int, int, int)`

@@ -198,7 +198,8 @@ int choose_path(const DeviceCtx* ctx, const Problem& p)
     const int forced = current_path();
     if (forced == INT4L_PATH_SKINNY) return skinny_supports(ctx, p) ? INT4L_PATH_SKINNY : INT4L_PATH_TCGEN05;
     if (forced != INT4L_PATH_AUTO) return forced;
-    if (skinny_supports(ctx, p)) return INT4L_PATH_SKINNY;
+    // Measured: from m = 33 upwards the tensor-memory kernel with 128-wide tiles is at least as fast.
+    if (p.m <= 32 && skinny_supports(ctx, p)) return INT4L_PATH_SKINNY;
     return INT4L_PATH_TCGEN05;
 }
 

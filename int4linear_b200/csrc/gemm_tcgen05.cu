@@ -488,18 +488,28 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
             return tma_store ? launch_cfg<Cfg256x2W, true>(ctx, p, stream) : launch_cfg<Cfg256x2W, false>(ctx, p, stream);
         return tma_store ? launch_cfg<Cfg128W, true>(ctx, p, stream) : launch_cfg<Cfg128W, false>(ctx, p, stream);
     }
+    // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
+    // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile
+    // re-expands X less often per output, a narrower one fills more SMs when the problem is small.
     const long long tiles_m = (p.m + kBM - 1) / kBM;
     auto tiles = [&](int bn) { return tiles_m * ((p.n + bn - 1) / bn); };
-    int bn = 256;
-    if (tiles(256) < ctx->sm_count) bn = 128;
-    if (bn == 128 && tiles(128) < ctx->sm_count) bn = 64;
-    const int forced = forced_tile_n();
-    if (forced == 64 || forced == 128 || forced == 256) bn = forced;
-    // CTA pairs once there are at least as many 256 x 256 tiles as pairs (and more than one
-    // row block, or the second CTA of each pair would multiply zeros).
+    auto whole_waves = [](long long t, int workers) { return static_cast<double>((t + workers - 1) / workers); };
     const long long pair_tiles = ((p.m + 255) / 256) * static_cast<long long>((p.n + 255) / 256);
-    bool pairs = p.m > 128 && pair_tiles >= ctx->max_pairs;
-    if (forced != 0) pairs = false;
+    // pairs: the last wave may run as half-width items (tail splitting), hence half-wave steps
+    const double pair_waves = pair_tiles <= ctx->max_pairs
+                                  ? 1.0
+                                  : static_cast<double>((2 * pair_tiles + ctx->max_pairs - 1) / ctx->max_pairs) / 2.0;
+    const double cost_pairs = p.m > 128 ? pair_waves * 1.0 : 1e30;  // a lone row block would leave CTA 1 idle
+    const double cost256 = whole_waves(tiles(256), ctx->sm_count) * 1.25;
+    const double cost128 = whole_waves(tiles(128), ctx->sm_count) * 0.90;
+    const double cost64 = whole_waves(tiles(64), ctx->sm_count) * 0.72;
+    int bn = 256;
+    double best = cost256;
+    if (cost128 < best) { best = cost128; bn = 128; }
+    if (cost64 < best) { best = cost64; bn = 64; }
+    bool pairs = cost_pairs <= best;
+    const int forced = forced_tile_n();
+    if (forced == 64 || forced == 128 || forced == 256) { bn = forced; pairs = false; }
     if (forced_pairs() >= 0) pairs = forced_pairs() != 0;
     if (pairs && forced_pairs() == 2 && p.scaled.y16 == nullptr) return launch_tcgen05_ts(ctx, p, stream);
     if (pairs) return tma_store ? launch_cfg<Cfg256x2, true>(ctx, p, stream) : launch_cfg<Cfg256x2, false>(ctx, p, stream);
