@@ -211,6 +211,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--path", default="auto", choices=["auto", "tcgen05", "legacy", "skinny"],
                     help="force one kernel family of this library (default: shape dispatch)")
+    ap.add_argument("--variant", default="default", choices=["default", "two-pass", "prepared", "x-tmem"],
+                    help="opt-in variants of the tensor-memory path: expand pre-pass + byte GEMM, weights "
+                         "pre-expanded outside the timed region, X operand in tensor memory")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -281,8 +284,17 @@ def main():
         w_copies = [wd] + [wd.clone() for _ in range(copies - 1)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    if args.variant == "two-pass":
+        L.set_two_pass(1)
+    elif args.variant == "x-tmem":
+        L.set_tuning(0, False, 2)
+    w_prepared = L.prepare_weights(wd) if args.variant == "prepared" else None
+
     def step(i):
-        L.linear(xd, w_copies[i % len(w_copies)], out=yd)
+        if w_prepared is not None:
+            L.linear_prepared(xd, w_prepared, out=yd)
+        else:
+            L.linear(xd, w_copies[i % len(w_copies)], out=yd)
 
     def barrier():
         torch.cuda.synchronize()
@@ -430,6 +442,7 @@ def main():
                        "shard": f"{world} x (M={m}, N={n_local}, K={k}), W and Y split along N, X replicated",
                        "l2": "256 MiB flush write before every timed launch" if not rotate
                              else f"{len(w_copies)} rotating copies of W ({len(w_copies) * wp.nbytes >> 20} MiB > L2)",
+                       "variant": args.variant,
                        "kernel_path": args.path if args.path != "auto"
                        else {1: "tcgen05", 2: "legacy", 3: "skinny"}[L.path_for(m, n_local, k)]},
             "tops": tops, "algorithmic_gbs": gbs,
