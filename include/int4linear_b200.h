@@ -14,6 +14,8 @@
  * (the kernels multiply 16*x by 16*w in int32 and shift the sum back).
  * X, W and Y must be 16-byte aligned.  Any m and n are accepted.
  *
+ * The first call on a device sets that device up (a host-mapped status word, kernel
+ * attributes, one driver entry point); issue it before any CUDA-graph capture.
  * All functions are thread-safe per device.  Nothing here falls back to a
  * CPU implementation: without an sm_100 GPU every compute entry point fails
  * with INT4L_ERR_NO_DEVICE.
@@ -150,6 +152,13 @@ int int4_linear_unpack_i32(const void* src_d, int* dst_d, int rows, int cols, vo
 /* Status of the most recent call on the current device; also polls the word
  * the kernels raise when a bounded wait expires (and clears it). */
 int int4_linear_last_status(void);
+
+/* Self-test of the in-kernel failure handling, safe to run on a shared GPU: launches one warp
+ * that waits for at most budget_ms (1..100) on a barrier nothing will ever signal, exactly as a
+ * GEMM kernel would after a lost arrival.  The kernel must return by itself; afterwards
+ * int4_linear_last_status() reports INT4L_ERR_DEVICE_TIMEOUT once and the device stays usable.
+ * Returns INT4L_OK when the kernel was run and came back. */
+int int4_linear_selftest_timeout(int budget_ms);
 
 /* Static string for a status code. */
 const char* int4_linear_status_string(int status);

@@ -21,6 +21,7 @@ SYMBOLS = {
     "int4_linear_pack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_pack_i8": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_unpack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
+    "int4_linear_selftest_timeout": (_I, [_I]),
     "int4_linear_last_status": (_I, []),
     "int4_linear_status_string": (ctypes.c_char_p, [_I]),
     "int4_linear_set_path": (_I, [_I]),

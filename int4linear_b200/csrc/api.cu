@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "common.h"
+#include "ptx.cuh"
 
 namespace i4l {
 
@@ -314,6 +315,24 @@ int host_pipelined(DeviceCtx* ctx, const void* x_h, const void* w_h, void* y_h, 
 
 }  // namespace
 
+// Self-test of the failure path: one warp waits, with the given budget, on an mbarrier that
+// nothing ever arrives at -- the situation a wrong descriptor or a lost arrival would create in a
+// GEMM kernel -- and must come back by itself and raise the status word like the real kernels do.
+__global__ void selftest_timeout_kernel(int* status, unsigned long long budget_ns)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const bool arrived = mbar_wait(smem_u32(&bar), 0, &abort_flag, budget_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && !arrived && abort_flag) atomicExch(status, INT4L_ERR_DEVICE_TIMEOUT);
+}
+
 }  // namespace i4l
 
 using namespace i4l;
@@ -467,6 +486,18 @@ int int4_linear_unpack_i32(const void* src_d, int* dst_d, int rows, int cols, vo
     if (ctx) rc = launch_unpack(ctx, src_d, dst_d, rows, cols, static_cast<cudaStream_t>(stream));
     t_last_status = rc;
     return rc;
+}
+
+int int4_linear_selftest_timeout(int budget_ms)
+{
+    if (budget_ms < 1 || budget_ms > 100) return INT4L_ERR_INVALID_ARG;
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) return rc;
+    selftest_timeout_kernel<<<1, 32>>>(ctx->status_dev, static_cast<unsigned long long>(budget_ms) * 1000000ull);
+    count_launch();
+    if (cudaGetLastError() != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+    return INT4L_OK;
 }
 
 int int4_linear_last_status(void)

@@ -115,7 +115,8 @@ constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
 // Wait for the phase with the given parity to complete.  Returns false (after
 // raising *abort_flag, a shared-memory word all roles poll) if the budget runs
 // out or another thread already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t budget_ns = kWaitBudgetNs) {
     uint64_t t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -123,7 +124,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitBudgetNs) { *abort_flag = 1; return false; }
+            else if (now - t0 > budget_ns) { *abort_flag = 1; return false; }
         }
     }
 }

@@ -291,3 +291,24 @@ def test_scaled_bf16_epilogue(cuda, shape):
     # unscaled: bf16 of the exact integers (all |acc| here are exactly representable up to rounding)
     exact = torch.from_numpy(acc).to(torch.bfloat16).float().numpy()
     assert np.array_equal(got, exact)
+
+
+def test_bounded_wait_reports_and_recovers(cuda):
+    """Failure handling without a fault: a wait that can never be satisfied runs out after its
+    budget, the kernel returns, the status word says so once, and the next launch works."""
+    import time
+    import torch
+    from int4linear_b200 import _lib
+    lib = _lib.load()
+    assert lib.int4_linear_last_status() == 0
+    t0 = time.perf_counter()
+    assert lib.int4_linear_selftest_timeout(20) == 0
+    assert time.perf_counter() - t0 < 2.0           # came back by itself, promptly
+    assert lib.int4_linear_last_status() == 5       # INT4L_ERR_DEVICE_TIMEOUT, reported ...
+    assert lib.int4_linear_selftest_timeout(0) == 1 # (argument check)
+    m, n, k = 200, 136, 160
+    x, w, xp, wp = make_case(m, n, k, seed=3)
+    y = L.linear(torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda))
+    torch.cuda.synchronize()
+    assert lib.int4_linear_last_status() == 0       # ... once; the device is still usable
+    assert O.is_same(y.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))
