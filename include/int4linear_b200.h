@@ -198,7 +198,8 @@ int int4_linear_set_overlap(int mode);
  * tensor-memory family runs; 0 or -1 = fused single-kernel path only (default; no scratch).
  * Returns INT4L_OK, or INT4L_ERR_INVALID_ARG for any other mode (setting unchanged).
  * Environment: INT4L_TWO_PASS.  Because the first use of a larger shape allocates, make that
- * call before capturing a CUDA graph. */
+ * call before capturing a CUDA graph.  The scratch is one buffer per device: two-pass launches
+ * that could run concurrently on one device (different streams) must not be issued. */
 int int4_linear_set_two_pass(int mode);
 
 /* Which family the dispatcher would use for a shape (INT4L_PATH_*). */

@@ -225,16 +225,9 @@ int run_two_pass(DeviceCtx* ctx, const Problem& p, void* scratch, cudaStream_t s
     return launch_tcgen05_s8(ctx, p, xb, wb, stream);
 }
 
-// Whether the two-pass path pays for a shape: the pre-pass moves 1.5 * (m + n) * k bytes through
-// HBM, the GEMM it speeds up does 2 * m * n * k operations, so it needs both m and n large.
-bool two_pass_wanted(const Problem& p)
-{
-    // Measured on B200: within +-5 % of the fused kernel from 8192 x 8192 outputs upwards
-    // (K = 8192) and slower below, for 2.5x the operand traffic -- so it is never chosen
-    // automatically; callers opt in with int4_linear_set_two_pass(1).
-    (void)p;
-    return two_pass_mode() == 1;
-}
+// The two-pass path is opt-in only: measured on B200 it equals the fused kernel from 8192 x 8192
+// outputs upwards (K = 8192) and is slower below, for 2.5x the operand traffic and a scratch buffer.
+bool two_pass_wanted() { return two_pass_mode() == 1; }
 
 int dispatch(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
@@ -243,7 +236,7 @@ int dispatch(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         case INT4L_PATH_LEGACY: return launch_legacy(ctx, p, stream);
         default: break;
     }
-    if (two_pass_wanted(p) && forced_pairs() < 0 && forced_tile_n() == 0) {
+    if (two_pass_wanted() && forced_pairs() < 0 && forced_tile_n() == 0) {
         const size_t need = (static_cast<size_t>(p.m) + p.n) * p.k;
         bool have;
         {
