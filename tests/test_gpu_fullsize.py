@@ -76,3 +76,32 @@ def test_headline_shape_rows_and_shards(cuda):
     w = L.unpack_bytes(wp).astype(np.int32)
     ref = O.linear_ref(x, w)
     assert O.is_same(yd[torch.from_numpy(rows).long().to(cuda)].cpu().numpy(), ref)
+
+
+def test_large_config_c5_bit_exact(cuda):
+    """c5 = 8192 x 28672 x 8192, the N-sharded config: the whole 896 MiB result is compared with the
+    float32-BLAS restatement (exact at these magnitudes) in row blocks, sampled rows with the
+    oracle's integer loop, and the 8-way N-shard results with the matching columns."""
+    import torch
+    m, n, k = 8192, 28672, 8192
+    xp = L.uniform_s4_packed(0xA005, m, k)
+    wp = L.uniform_s4_packed(0xB005, n, k)
+    xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+    yd = L.linear(xd, wd)
+    torch.cuda.synchronize()
+    assert L.last_status() == 0
+    for s in range(8):  # what each of 8 GPUs would compute
+        lo, hi = s * (n // 8), (s + 1) * (n // 8)
+        ys = L.linear(xd, wd[lo:hi].contiguous())
+        assert bool((ys == yd[:, lo:hi]).all())
+    torch.cuda.synchronize()
+    assert L.last_status() == 0
+    y = yd.cpu().numpy()
+    w = L.unpack_bytes(wp)
+    rows = np.array([0, 255, 256, 4099, 8191], dtype=np.int32)
+    x_rows = L.unpack_bytes(xp[rows]).astype(np.int32)
+    assert O.is_same(y[rows], O.linear_ref(x_rows, w.astype(np.int32)))
+    wf = w.astype(np.float32)
+    for r0 in range(0, m, 1024):
+        xf = L.unpack_bytes(xp[r0:r0 + 1024]).astype(np.float32)
+        assert O.is_same(y[r0:r0 + 1024], (xf @ wf.T).astype(np.int32)), f"rows {r0}..{r0 + 1023}"
