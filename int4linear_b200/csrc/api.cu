@@ -18,6 +18,7 @@ constexpr int kMaxDevices = 64;
 DeviceCtx g_ctx[kMaxDevices];
 bool g_ctx_ready[kMaxDevices];
 std::mutex g_mutex;          // contexts and the host-buffer staging
+std::mutex g_tm_mutex;       // tensor-map cache
 std::mutex g_scratch_mutex;  // two-pass scratch (taken inside dispatch, which may run under g_mutex)
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_path{-1};       // -1 = not yet read from the environment
@@ -178,6 +179,17 @@ int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int e
                        uint64_t inner_elems, uint64_t rows, uint64_t row_pitch_bytes,
                        uint32_t box_inner, uint32_t box_rows, bool swizzle128, bool swizzle64)
 {
+    const int swizzle = swizzle128 ? 2 : (swizzle64 ? 1 : 0);
+    {
+        std::lock_guard<std::mutex> lock(g_tm_mutex);
+        for (const TensorMapEntry& e : ctx->tm_cache) {
+            if (e.base == base && e.inner == inner_elems && e.rows == rows && e.pitch == row_pitch_bytes &&
+                e.box_inner == box_inner && e.box_rows == box_rows && e.elem_bytes == elem_bytes && e.swizzle == swizzle) {
+                *out = e.map;
+                return INT4L_OK;
+            }
+        }
+    }
     const cuuint64_t dims[2] = {inner_elems, rows};
     const cuuint64_t strides[1] = {row_pitch_bytes};
     const cuuint32_t box[2] = {box_inner, box_rows};
@@ -187,7 +199,16 @@ int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int e
         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
         swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? INT4L_OK : INT4L_ERR_CUDA;
+    if (r != CUDA_SUCCESS) return INT4L_ERR_CUDA;
+    // A tensor map describes addresses and shapes only, never contents, so a remembered one stays
+    // valid for as long as the same pointer denotes an allocation of at least that extent.
+    std::lock_guard<std::mutex> lock(g_tm_mutex);
+    TensorMapEntry& e = ctx->tm_cache[ctx->tm_next];
+    ctx->tm_next = (ctx->tm_next + 1) % DeviceCtx::kTensorMapCache;
+    e.base = base; e.inner = inner_elems; e.rows = rows; e.pitch = row_pitch_bytes;
+    e.box_inner = box_inner; e.box_rows = box_rows; e.elem_bytes = elem_bytes; e.swizzle = swizzle;
+    e.map = *out;
+    return INT4L_OK;
 }
 
 bool skinny_supports(const DeviceCtx* ctx, const Problem& p);

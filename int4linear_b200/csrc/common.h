@@ -37,8 +37,21 @@ struct Problem {
     ScaledOut scaled;
 };
 
+// One remembered tensor map: encoding costs a driver call of a microsecond or two, and a
+// serving loop presents the same few (pointer, shape, box) combinations over and over.
+struct TensorMapEntry {
+    const void* base = nullptr;
+    uint64_t inner = 0, rows = 0, pitch = 0;
+    uint32_t box_inner = 0, box_rows = 0;
+    int elem_bytes = 0, swizzle = 0;
+    CUtensorMap map;
+};
+
 // Per-device state created on the first call on that device.
 struct DeviceCtx {
+    static constexpr int kTensorMapCache = 32;
+    TensorMapEntry tm_cache[kTensorMapCache];
+    int tm_next = 0;  // round-robin replacement
     int device = -1;
     int sm_count = 0;
     int max_pairs = 0;  // co-resident 2-CTA clusters of the GEMM kernel

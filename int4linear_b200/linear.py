@@ -95,28 +95,41 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias
     import torch
     if not (x_packed.is_cuda and w_packed.is_cuda):
         raise ValueError("linear() needs CUDA tensors; there is no CPU implementation")
-    xb = x_packed.contiguous().view(torch.uint8)
-    wb = w_packed.contiguous().view(torch.uint8)
-    m, n = xb.shape[0], wb.shape[0]
+    # Row width in bytes without materialising views (this function sits on the per-token path).
+    if not (x_packed.is_contiguous() and w_packed.is_contiguous()):
+        x_packed, w_packed = x_packed.contiguous(), w_packed.contiguous()
+    m, n = x_packed.shape[0], w_packed.shape[0]
+    xbytes = x_packed.shape[1] * x_packed.element_size()
+    wbytes = w_packed.shape[1] * w_packed.element_size()
     if k is None:
-        k = xb.shape[1] * 2
-    if xb.shape[1] * 2 != k or wb.shape[1] * 2 != k:
+        k = xbytes * 2
+    if xbytes * 2 != k or wbytes * 2 != k:
         raise ValueError("packed widths do not match k")
     if out is None:
-        out = torch.empty((m, n), dtype=torch.int32, device=xb.device)
-    with torch.cuda.device(xb.device):
-        if bias is None:
-            launch(LinearArgs(xb.data_ptr(), wb.data_ptr(), out.data_ptr(), m, n, k), stream)
-        else:
-            if bias.dtype != torch.int32 or bias.numel() != n or not bias.is_cuda:
-                raise ValueError("bias must be a CUDA int32 tensor with n elements")
-            bias = bias.contiguous()
-            handle = (stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)) if stream is not None \
-                else torch.cuda.current_stream().cuda_stream
-            st = _lib.load().int4_linear_bias_launch_async(xb.data_ptr(), wb.data_ptr(), bias.data_ptr(),
-                                                           out.data_ptr(), m, n, k, handle)
-            if st != 0:
-                raise Int4LinearError(st, "int4_linear_bias_launch_async")
+        out = torch.empty((m, n), dtype=torch.int32, device=x_packed.device)
+    if stream is None:
+        handle = torch.cuda.current_stream(x_packed.device).cuda_stream
+    else:
+        handle = stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+    if bias is not None:
+        if bias.dtype != torch.int32 or bias.numel() != n or not bias.is_cuda:
+            raise ValueError("bias must be a CUDA int32 tensor with n elements")
+        bias = bias.contiguous()
+    lib = _lib.load()
+    dev = x_packed.device.index
+    switch = dev is not None and dev != torch.cuda.current_device()
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        st = lib.int4_linear_bias_launch_async(x_packed.data_ptr(), w_packed.data_ptr(),
+                                               bias.data_ptr() if bias is not None else None,
+                                               out.data_ptr(), m, n, k, handle)
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_bias_launch_async")
     return out
 
 
