@@ -370,6 +370,7 @@ def main():
 
     # ---- optional: all-gather of the Y shards (reported separately, never in `value`)
     gather_ms = None
+    gather_cmp = None
     if args.gather and world > 1:
         out = torch.empty((world, m, n_local), dtype=torch.int32, device=dev)
         for _ in range(2):
@@ -384,6 +385,36 @@ def main():
         g = torch.tensor([e0.elapsed_time(e1) / 5], dtype=torch.float64, device=dev)
         dist.all_reduce(g, op=dist.ReduceOp.MAX)
         gather_ms = float(g.item())
+
+        # GEMM followed by the all-gather, against the GEMM whose epilogue stores straight into
+        # every rank's full-width Y over NVLink (plus the device-side rank barriers around it).
+        from int4linear_b200.sharding import FusedGatherBuffer, Shard
+
+        def timed(fn, reps=5):
+            for _ in range(2):
+                fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            barrier()
+            v = torch.tensor([a.elapsed_time(b) / reps], dtype=torch.float64, device=dev)
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+            return float(v.item())
+
+        def unfused():
+            L.linear(xd, wd, out=yd)
+            dist.all_gather_into_tensor(out, yd)
+
+        fused_buf = FusedGatherBuffer(m, n_total, dev)
+        shard = Shard(rank, world, row_start, n_local)
+        unfused_ms = timed(unfused)
+        fused_ms = timed(lambda: fused_buf.run(xd, wd, shard, k))
+        same = torch.equal(fused_buf.y.view(m, world, n_local), out.permute(1, 0, 2))
+        gather_cmp = {"gemm_then_all_gather_ms": unfused_ms, "fused_gather_ms": fused_ms,
+                      "fused_equals_all_gather": bool(same)}
 
     # ---- end to end through the host-buffer entry point
     e2e = None
@@ -458,6 +489,7 @@ def main():
         line["e2e"] = e2e
     if gather_ms is not None:
         line["all_gather_ms"] = gather_ms
+        line["gather"] = gather_cmp
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_reference_sample(m, n_total, k)
     print(json.dumps(line))

@@ -93,6 +93,22 @@ int int4_linear_scaled_launch_async(const void* x_packed_d, const void* w_packed
                                     int m, int n, int k, void* stream);
 
 /*
+ * N-sharded GEMM fused with the all-gather of its result.  This rank holds n_local rows of W
+ * (columns [col_offset, col_offset + n_local) of the full Y) and the full X; y_full_ptrs is a HOST
+ * array of `world` (<= 8) device pointers to the m x n_total int32 result buffer of every rank
+ * of the node -- the rank's own buffer and its peers' buffers mapped into this process (CUDA
+ * IPC / symmetric memory).  The kernel's epilogue stores the rank's column block into all of them
+ * with TMA stores over NVLink while later tiles are still being computed; no multicast and no
+ * loads from peer memory are involved.  Every rank calls this with its own shard; the full Y is
+ * complete on a rank once ALL ranks' kernels have finished (synchronise the ranks afterwards,
+ * e.g. with a barrier).  Needs n_local % 32 == 0, col_offset % 32 == 0, n_total % 4 == 0.
+ * No reference counterpart (the reference is single-GPU).
+ */
+int int4_linear_launch_gather_async(const void* x_packed_d, const void* w_shard_packed_d, const int* bias_d,
+                                    void* const* y_full_ptrs, int world, int col_offset,
+                                    int m, int n_local, int n_total, int k, void* stream);
+
+/*
  * Weight-stationary pre-layout.  int4_linear_prepare_weights expands a packed W (n rows of k/2
  * bytes) once into n rows of k bytes in the byte order the GEMM's tensor-core stage consumes
  * (w_expanded_d: n * k bytes, 16-byte aligned); int4_linear_launch_prepared_async then runs the

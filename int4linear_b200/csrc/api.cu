@@ -419,6 +419,23 @@ int int4_linear_scaled_launch_async(const void* x, const void* w, const float* r
     return rc;
 }
 
+int int4_linear_launch_gather_async(const void* x, const void* w_shard, const int* bias_d, void* const* y_full_ptrs,
+                                    int world, int col_offset, int m, int n_local, int n_total, int k, void* stream)
+{
+    if (!y_full_ptrs || world < 1 || world > 8 || n_total <= 0 || col_offset < 0) { t_last_status = INT4L_ERR_INVALID_ARG; return INT4L_ERR_INVALID_ARG; }
+    for (int d = 0; d < world; ++d)
+        if (!y_full_ptrs[d] || (reinterpret_cast<uintptr_t>(y_full_ptrs[d]) & 15u)) { t_last_status = INT4L_ERR_INVALID_ARG; return INT4L_ERR_INVALID_ARG; }
+    int rc = check_args(x, w_shard, y_full_ptrs[0], m, n_local, k);
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{x, w_shard, nullptr, m, n_local, k, bias_d};
+    GatherDst g{y_full_ptrs, world, col_offset, n_total};
+    rc = launch_tcgen05_gather(ctx, p, g, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
 void int4_linear_launch(void* x, void* w, void* y, int m, int n, int k)
 {
     int rc = int4_linear_launch_async(x, w, y, m, n, k, nullptr);

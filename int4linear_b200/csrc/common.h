@@ -86,10 +86,19 @@ int make_tensor_map_2d(DeviceCtx* ctx, CUtensorMap* out, const void* base, int e
                        uint64_t inner_elems, uint64_t rows, uint64_t row_pitch_bytes,
                        uint32_t box_inner, uint32_t box_rows, bool swizzle128, bool swizzle64 = false);
 
+// Destinations of the gathering GEMM: the full-width Y (m x n_total int32) of every rank.
+struct GatherDst {
+    void* const* y_full;  // `world` device pointers (this rank's own buffer and mapped peer buffers)
+    int world;
+    int col_offset;       // first column of this rank's block
+    int n_total;
+};
+
 // Kernel launchers.  Each returns an INT4L_* status; none of them synchronises.
 int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 // GEMM on operands already expanded to bytes (second pass of the two-pass path).
 int launch_tcgen05_s8(DeviceCtx* ctx, const Problem& p, const void* x_bytes, const void* w_bytes, cudaStream_t stream);
+int launch_tcgen05_gather(DeviceCtx* ctx, const Problem& p, const GatherDst& g, cudaStream_t stream);
 int launch_tcgen05_ts(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);  // X operand in tensor memory
 int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 int launch_legacy(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);

@@ -5,7 +5,8 @@
 // shifted right by 8 (arithmetic, exact), the optional int32 bias of its column is added, and
 // the 32 x 32 chunk goes out either
 //   * through a 128-byte-swizzled shared-memory staging buffer and one TMA store (which clips
-//     the M and N tails by itself); two staging buffers per warp alternate, and a buffer is
+//     the M and N tails by itself; `n_maps` destinations, each shifted right by `col_shift`
+//     columns); two staging buffers per warp alternate, and a buffer is
 //     reused only after the store group that read it has finished reading; or
 //   * with per-thread stores (any n, needed when the row pitch of Y is not a multiple of 16 B).
 // Replaces the reference's per-thread int2 stores, kernels/linear_v21.h:661-710.
@@ -21,7 +22,8 @@ namespace i4l {
 template <bool kTmaStore>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, int row0, int col0, int m, int n,
                                                   int* __restrict__ y, const int* __restrict__ bias,
-                                                  const CUtensorMap* tm_y, uint32_t stage0, uint32_t& chunk_no,
+                                                  const CUtensorMap* tm_y, int n_maps, int col_shift,
+                                                  uint32_t stage0, uint32_t& chunk_no,
                                                   int lane)
 {
     const int row = row0 + lane;
@@ -53,7 +55,9 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                tma_store_2d(tm_y, stg, col0 + c, row0);
+                // One store per destination matrix (one normally; every rank's copy of the full Y
+                // when the result is gathered through peer memory), all from the same staging tile.
+                for (int d = 0; d < n_maps; ++d) tma_store_2d(tm_y + d, stg, col_shift + col0 + c, row0);
                 tma_store_commit();
             }
             ++chunk_no;

@@ -84,15 +84,21 @@ struct Cfg {
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
+// Destination tensor maps of the gathering variant: the full Y of every rank of the node.
+constexpr int kMaxPeers = 8;
+struct PeerMaps {
+    CUtensorMap map[kMaxPeers];
+};
+
+// Kernel body.  y_maps[0 .. n_y_maps) are the TMA-store destinations: the caller's Y normally;
+// with peer gathering, every rank's full-width Y, this rank's block starting col_shift columns in.
 template <class C, bool kTmaStore>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
-                       const __grid_constant__ CUtensorMap tm_w,
-                       const __grid_constant__ CUtensorMap tm_wh,
-                       const __grid_constant__ CUtensorMap tm_y,
-                       int* __restrict__ y, int m, int n, int k,
-                       int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias,
-                       const ScaledOut so)
+__device__ __forceinline__ void
+gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_wh,
+                     const CUtensorMap* y_maps, int n_y_maps, int col_shift,
+                     int* __restrict__ y, int m, int n, int k,
+                     int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias,
+                     const ScaledOut& so)
 {
     constexpr int BN = C::kBN, P = C::kP, U = C::kU, CTAS = C::kCtas;
     extern __shared__ uint8_t smem_raw[];
@@ -133,7 +139,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
         mbar_init_fence();
         tma_prefetch_desc(&tm_x);
         tma_prefetch_desc(&tm_w);
-        if (kTmaStore) tma_prefetch_desc(&tm_y);
+        if (kTmaStore) tma_prefetch_desc(y_maps);
     }
     if (warp == 1) {
         tmem_alloc<CTAS>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
@@ -261,7 +267,7 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             if (!kTmaStore && so.y16 != nullptr)
                 drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
             else
-                drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
+                drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -358,6 +364,37 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
     }
 }
 
+template <class C, bool kTmaStore>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
+                       const __grid_constant__ CUtensorMap tm_w,
+                       const __grid_constant__ CUtensorMap tm_wh,
+                       const __grid_constant__ CUtensorMap tm_y,
+                       int* __restrict__ y, int m, int n, int k,
+                       int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias,
+                       const ScaledOut so)
+{
+    gemm_s4_tcgen05_body<C, kTmaStore>(tm_x, tm_w, tm_wh, &tm_y, 1, 0, y, m, n, k, tiles_m, tiles_n, split_from,
+                                       status, bias, so);
+}
+
+// GEMM fused with the all-gather of its result: the epilogue stores this rank's column block of Y
+// into the full-width Y of every rank of the node -- ordinary TMA stores whose destination
+// happens to be peer memory mapped over NVLink (no multicast, no loads from peers) -- so the
+// exchange overlaps the tiles still being computed instead of following the GEMM as a collective.
+template <class C>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_s4_tcgen05_gather_kernel(const __grid_constant__ CUtensorMap tm_x,
+                              const __grid_constant__ CUtensorMap tm_w,
+                              const __grid_constant__ CUtensorMap tm_wh,
+                              const __grid_constant__ PeerMaps peers, int n_peers, int col_shift,
+                              int m, int n, int k, int tiles_m, int tiles_n, int split_from, int* status,
+                              const int* __restrict__ bias)
+{
+    gemm_s4_tcgen05_body<C, true>(tm_x, tm_w, tm_wh, peers.map, n_peers, col_shift, nullptr, m, n, k, tiles_m, tiles_n,
+                                  split_from, status, bias, ScaledOut{});
+}
+
 using Cfg256 = Cfg<256, 3, 2, 1>;
 using Cfg128 = Cfg<128, 4, 3, 1>;
 using Cfg64 = Cfg<64, 4, 4, 1>;
@@ -377,7 +414,7 @@ bool tail_split_enabled()
 }
 
 template <class C, bool kTmaStore>
-int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
+int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const GatherDst* gather = nullptr)
 {
     const int tiles_m = (p.m + C::kTileM - 1) / C::kTileM;
     const int tiles_n = (p.n + C::kBN - 1) / C::kBN;
@@ -390,7 +427,7 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     else
         rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW, false);
     if (rc != INT4L_OK) return rc;
-    if (kTmaStore) {
+    if (kTmaStore && gather == nullptr) {
         rc = make_tensor_map_2d(ctx, &tm_y, p.y, 4, p.n, p.m, static_cast<uint64_t>(p.n) * 4, 32, 32, true);
         if (rc != INT4L_OK) return rc;
     } else {
@@ -424,9 +461,26 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_kernel<C, kTmaStore>, tm_x, tm_w, tm_wh, tm_y,
-                                       static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, split_from,
-                                       ctx->status_dev, p.bias, p.scaled);
+    cudaError_t e;
+    if constexpr (kTmaStore && !C::kPreW) {
+        if (gather != nullptr) {
+            PeerMaps peers;
+            for (int d = 0; d < gather->world; ++d) {
+                rc = make_tensor_map_2d(ctx, &peers.map[d], gather->y_full[d], 4, gather->n_total, p.m,
+                                        static_cast<uint64_t>(gather->n_total) * 4, 32, 32, true);
+                if (rc != INT4L_OK) return rc;
+            }
+            for (int d = gather->world; d < kMaxPeers; ++d) peers.map[d] = peers.map[0];
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_gather_kernel<C>, tm_x, tm_w, tm_wh, peers, gather->world,
+                                   gather->col_offset, p.m, p.n, p.k, tiles_m, tiles_n, split_from, ctx->status_dev, p.bias);
+            count_launch();
+            if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+            return INT4L_OK;
+        }
+    }
+    e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_kernel<C, kTmaStore>, tm_x, tm_w, tm_wh, tm_y,
+                           static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, split_from,
+                           ctx->status_dev, p.bias, p.scaled);
     count_launch();
     if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
     return INT4L_OK;
@@ -453,6 +507,10 @@ int setup_tcgen05(DeviceCtx* ctx)
     if (rc == INT4L_OK) rc = set_attr<Cfg256x2>();
     if (rc == INT4L_OK) rc = set_attr<Cfg256x2W>();
     if (rc == INT4L_OK) rc = set_attr<Cfg128W>();
+    if (rc == INT4L_OK && cudaFuncSetAttribute(gemm_s4_tcgen05_gather_kernel<Cfg256x2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               Cfg256x2::kSmemBytes) != cudaSuccess) rc = INT4L_ERR_CUDA;
+    if (rc == INT4L_OK && cudaFuncSetAttribute(gemm_s4_tcgen05_gather_kernel<Cfg128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               Cfg128::kSmemBytes) != cudaSuccess) rc = INT4L_ERR_CUDA;
     if (rc != INT4L_OK) return rc;
     // How many CTA pairs the device can hold at once (pairs must sit in one GPC-level
     // neighbourhood, so this can be below sm_count / 2).
@@ -516,6 +574,19 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     if (bn == 256) return tma_store ? launch_cfg<Cfg256, true>(ctx, p, stream) : launch_cfg<Cfg256, false>(ctx, p, stream);
     if (bn == 128) return tma_store ? launch_cfg<Cfg128, true>(ctx, p, stream) : launch_cfg<Cfg128, false>(ctx, p, stream);
     return tma_store ? launch_cfg<Cfg64, true>(ctx, p, stream) : launch_cfg<Cfg64, false>(ctx, p, stream);
+}
+
+// GEMM + all-gather through peer stores (see gemm_s4_tcgen05_gather_kernel).  p.n is this rank's
+// column count; p.y is not used.
+int launch_tcgen05_gather(DeviceCtx* ctx, const Problem& p, const GatherDst& g, cudaStream_t stream)
+{
+    if (g.world < 1 || g.world > kMaxPeers) return INT4L_ERR_INVALID_ARG;
+    // Store chunks are 32 columns wide: a block that ends inside a chunk would spill into the
+    // neighbouring rank's columns; TMA stores want a 16-byte row pitch.
+    if (p.n % 32 != 0 || g.col_offset % 32 != 0 || g.n_total % 4 != 0 || g.col_offset + p.n > g.n_total)
+        return INT4L_ERR_UNSUPPORTED;
+    if (p.m > 128) return launch_cfg<Cfg256x2, true>(ctx, p, stream, &g);
+    return launch_cfg<Cfg128, true>(ctx, p, stream, &g);
 }
 
 }  // namespace i4l

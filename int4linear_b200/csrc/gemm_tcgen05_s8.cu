@@ -178,7 +178,7 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
-            drain_accumulator<kTmaStore>(t_addr, BN, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
+            drain_accumulator<kTmaStore>(t_addr, BN, row0, col0, m, n, y, bias, &tm_y, 1, 0, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {

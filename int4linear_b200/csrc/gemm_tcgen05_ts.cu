@@ -182,7 +182,7 @@ gemm_s4_tcgen05_ts_kernel(const __grid_constant__ CUtensorMap tm_x,
             const int row0 = (tm * 2 + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * kBN;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * kBN;
-            drain_accumulator<kTmaStore>(t_addr, kBN, row0, col0, m, n, y, bias, &tm_y, stage0, chunk_no, lane);
+            drain_accumulator<kTmaStore>(t_addr, kBN, row0, col0, m, n, y, bias, &tm_y, 1, 0, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tm_empty(buf), 0);

@@ -251,3 +251,40 @@ def path_for(m: int, n: int, k: int) -> int:
     if r < 0:
         raise Int4LinearError(-r, "int4_linear_path_for")
     return r
+
+
+def linear_gather(x_packed, w_shard_packed, y_full_ptrs, col_offset: int, n_total: int,
+                  k: int | None = None, stream=None, bias=None) -> None:
+    """This rank's column block of Y = X @ W^T, stored by the kernel's epilogue into the full
+    [m, n_total] int32 result of EVERY rank: `y_full_ptrs` lists one device address per rank
+    (this rank's own buffer and its peers' buffers mapped into this process).  Asynchronous;
+    the full Y is complete on a rank only after all ranks' launches have finished.  No
+    reference counterpart (the reference is single-GPU)."""
+    import ctypes
+    import torch
+    if not (x_packed.is_cuda and w_shard_packed.is_cuda):
+        raise ValueError("linear_gather() needs CUDA tensors; there is no CPU implementation")
+    x_packed, w_shard_packed = x_packed.contiguous(), w_shard_packed.contiguous()
+    m, n_local = x_packed.shape[0], w_shard_packed.shape[0]
+    xbytes = x_packed.shape[1] * x_packed.element_size()
+    if k is None:
+        k = xbytes * 2
+    if xbytes * 2 != k or w_shard_packed.shape[1] * w_shard_packed.element_size() * 2 != k:
+        raise ValueError("packed widths do not match k")
+    ptrs = [int(a) for a in y_full_ptrs]
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    if stream is None:
+        handle = torch.cuda.current_stream(x_packed.device).cuda_stream
+    else:
+        handle = stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+    if bias is not None:
+        if bias.dtype != torch.int32 or bias.numel() != n_local or not bias.is_cuda:
+            raise ValueError("bias must be a CUDA int32 tensor with n_local elements")
+        bias = bias.contiguous()
+    lib = _lib.load()
+    with torch.cuda.device(x_packed.device):
+        st = lib.int4_linear_launch_gather_async(x_packed.data_ptr(), w_shard_packed.data_ptr(),
+                                                 bias.data_ptr() if bias is not None else None,
+                                                 arr, len(ptrs), col_offset, m, n_local, n_total, k, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_launch_gather_async")

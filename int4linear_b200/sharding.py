@@ -103,8 +103,51 @@ class ShardedInt4Linear:
         self.w = w_shard_packed
         self.n_total, self.k, self.align = n_total, k, align
 
-    def forward(self, x_packed, gather: bool = False):
+        self._fused = {}  # m -> FusedGatherBuffer
+
+    def forward(self, x_packed, gather: bool | str = False):
+        """gather=False: this rank's columns.  gather=True: full Y through an NCCL all-gather
+        after the GEMM.  gather="fused": full Y written by the GEMM's own epilogue into every
+        rank's symmetric result buffer (one kernel, no collective); the returned tensor is
+        that buffer, reused by the next call with the same m."""
+        if gather == "fused" and self.world > 1:
+            m = x_packed.shape[0]
+            buf = self._fused.get(m)
+            if buf is None:
+                buf = self._fused[m] = FusedGatherBuffer(m, self.n_total, x_packed.device, self.group)
+            return buf.run(x_packed, self.w, self.shard, self.k)
         y = forward_local(x_packed, self.w, self.k)
         if gather and self.world > 1:
             return gather_columns(y, self.n_total, self.group, self.align)
         return y
+
+
+class FusedGatherBuffer:
+    """The full [m, n_total] int32 result of every rank, allocated as symmetric memory so that
+    each rank holds an address for every peer's copy.  `run` launches the gathering GEMM
+    (this rank's column block stored into all copies by the kernel's epilogue over NVLink) and
+    then synchronises the ranks on the device, after which the local copy is complete.
+
+    The exchange is plain stores to peer memory: no multicast, no loads from peers, no waits
+    inside the GEMM kernel; the rank synchronisation is the symmetric-memory barrier, which runs
+    as its own kernel after the GEMM on the same stream."""
+
+    def __init__(self, m: int, n_total: int, device, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.m, self.n_total = m, n_total
+        self.y = symm.empty((m, n_total), dtype=torch.int32, device=device)
+        self.handle = symm.rendezvous(self.y, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.world = self.handle.world_size
+
+    def run(self, x_packed, w_shard_packed, shard: Shard, k: int | None = None, bias=None):
+        from .linear import linear_gather
+        # Nobody may still be reading the previous result when peers start overwriting it.
+        self.handle.barrier(channel=0)
+        if shard.rows:
+            linear_gather(x_packed, w_shard_packed, self.ptrs, shard.row_start, self.n_total, k=k, bias=bias)
+        self.handle.barrier(channel=1)
+        return self.y
