@@ -110,6 +110,8 @@ class ShardedInt4Linear:
         after the GEMM.  gather="fused": full Y written by the GEMM's own epilogue into every
         rank's symmetric result buffer (one kernel, no collective); the returned tensor is
         that buffer, reused by the next call with the same m."""
+        if gather == "fused" and self.world > 1 and not self._fused_ok():
+            gather = True  # every rank takes the same decision: it depends on the global split only
         if gather == "fused" and self.world > 1:
             m = x_packed.shape[0]
             buf = self._fused.get(m)
@@ -120,6 +122,13 @@ class ShardedInt4Linear:
         if gather and self.world > 1:
             return gather_columns(y, self.n_total, self.group, self.align)
         return y
+
+
+    def _fused_ok(self) -> bool:
+        """The gathering kernel stores 32-column chunks: every shard must start and end on a
+        32-column boundary and rows of Y must be 16-byte multiples."""
+        return self.n_total % 4 == 0 and all(
+            s.rows % 32 == 0 and s.row_start % 32 == 0 for s in all_shards(self.n_total, self.world, self.align))
 
 
 class FusedGatherBuffer:

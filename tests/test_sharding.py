@@ -37,6 +37,19 @@ def test_shard_is_contiguous_view():
     assert v.shape[0] == s.rows and v[0, 0] == w[s.row_start, 0]
 
 
+def test_fused_gather_geometry_rule():
+    """The fused gather is used only when every shard starts and ends on a 32-column boundary;
+    the decision depends on the global split alone, so all ranks agree."""
+    class _Probe(S.ShardedInt4Linear):
+        def __init__(self, n_total, world, align=256):
+            self.n_total, self.world, self.align = n_total, world, align
+    assert _Probe(28672, 8)._fused_ok()
+    assert _Probe(8192, 2)._fused_ok()
+    assert _Probe(1536, 2)._fused_ok()
+    assert not _Probe(1000, 2)._fused_ok()     # last shard ends off a 32-column boundary
+    assert not _Probe(28672 + 2, 4)._fused_ok()  # row pitch of Y not a 16-byte multiple
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
