@@ -128,6 +128,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
     const uint32_t cta_rank = CTAS == 2 ? cluster_cta_rank() : 0u;
     const int worker = CTAS == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
     const int workers = CTAS == 2 ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
+    I4L_TRACE_CLK(0);
 
     if (tid == 0) {
         for (int i = 0; i < P; ++i) { mbar_init(pk_full(i), 1); mbar_init(pk_empty(i), kWarpsPerGroup); }
@@ -348,6 +349,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
     // ------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    I4L_TRACE_CLK(1);
     if (*abort_flag) {
         // Something never arrived.  Report, give copies in flight time to land,
         // then release tensor memory so the SM stays usable.
