@@ -130,26 +130,49 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
     const int workers = CTAS == 2 ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
     I4L_TRACE_CLK(0);
 
-    if (tid == 0) {
-        for (int i = 0; i < P; ++i) { mbar_init(pk_full(i), 1); mbar_init(pk_empty(i), kWarpsPerGroup); }
-        // up_full and tm_empty of CTA 0 collect the arrivals of both CTAs of a pair.
-        for (int i = 0; i < U; ++i) { mbar_init(up_full(i), kWarpsPerGroup * CTAS); mbar_init(up_empty(i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(tm_full(i), 1); mbar_init(tm_empty(i), 4 * CTAS); }
-        for (int i = 0; i < U; ++i) mbar_init(w_full(i), 1);
-        *abort_flag = 0;
+    // Barrier set-up by the lanes of warp 2 in parallel (one barrier each; a single thread takes
+    // over a thousand cycles for the two dozen of them), tensor-map prefetch by thread 0.
+    if (warp == 2) {
+        static_assert(C::kNumBarriers <= 32, "one lane per barrier");
+        if (lane < C::kNumBarriers) {
+            // pk_full | pk_empty | up_full | up_empty | tm_full | tm_empty | w_full.  up_full and
+            // tm_empty of CTA 0 collect the arrivals of both CTAs of a pair.
+            uint32_t count = 1;
+            if (lane >= P && lane < 2 * P) count = kWarpsPerGroup;
+            else if (lane >= 2 * P && lane < 2 * P + U) count = kWarpsPerGroup * CTAS;
+            else if (lane >= 2 * P + 2 * U + 2 && lane < 2 * P + 2 * U + 4) count = 4 * CTAS;
+            mbar_init(bar_base + 8u * lane, count);
+        }
+        if (lane == 0) *abort_flag = 0;
         mbar_init_fence();
+    } else if (tid == 0) {
         tma_prefetch_desc(&tm_x);
         tma_prefetch_desc(&tm_w);
         if (kTmaStore) tma_prefetch_desc(y_maps);
     }
-    if (warp == 1) {
-        tmem_alloc<CTAS>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
-        tmem_relinquish<CTAS>();
+    // Start-up order.  The TMA producer and the unpack warps need only this CTA's barriers, so they
+    // start right after the CTA-wide barrier; the tensor-memory allocation (warp 1) is awaited
+    // only by the warps that use tensor memory (named barrier 1 over warps 1-5), and the pair's
+    // cluster barrier -- "the other CTA's barriers exist" -- is split into an arrive here and a
+    // wait in each role just before its first access to the peer.
+    __syncthreads();
+    if (tid == 0) I4L_TRACE_PUT(0, 1, 3);
+    if constexpr (CTAS == 2) {
+        if (warp == 0) cluster_arrive_relaxed(); else cluster_arrive_release();
     }
-    tc_fence_before_sync();
-    if constexpr (CTAS == 2) cluster_sync_all(); else __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) I4L_TRACE_PUT(0, 2, 2);
+    uint32_t tmem_base = 0;
+    if (warp >= 1 && warp < 6) {
+        if (warp == 1) {
+            tmem_alloc<CTAS>(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+            tmem_relinquish<CTAS>();
+            tc_fence_before_sync();
+        }
+        named_barrier_sync(1, 160);
+        tc_fence_after_sync();
+        tmem_base = *tmem_slot;
+        if constexpr (CTAS == 2) cluster_wait();
+    }
 
     // Work items: tiles [0, split_from) as they are; each later tile as two half-width items, so
     // that a short last wave costs half a tile time (see launch_cfg).
@@ -212,6 +235,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 }
             }
         }
+        if constexpr (CTAS == 2) cluster_wait_divergent();  // the producer never touches the peer
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------- UMMA issuer
@@ -293,6 +317,9 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         static_assert(kChunks % kGroupThreads == 0, "unpack loop must divide evenly");
         uint32_t it = 0;
         bool alive = true;
+        // The pair's barrier completes long before the first TMA data arrives, so waiting for it
+        // here (warp still convergent) costs nothing.
+        if constexpr (CTAS == 2) cluster_wait();
         for (int item = worker; alive && item < num_items; item += workers) {
             // 16-byte chunks to convert in this item's stages (a half-width item has fewer W rows)
             const int chunks = C::kPreW ? kChunks : (item < split_from ? kChunks : (kBM + C::kRowsW / 2) * 4);

@@ -60,6 +60,28 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// The two halves of the same barrier, for code that has useful work between them.  Every thread
+// executes an arrive and a wait exactly once.
+// Arrive: warp-convergent forms.  `relaxed` is for warps that have written nothing the peer will
+// read (a release at cluster scope costs on the order of a thousand cycles).
+__device__ __forceinline__ void cluster_arrive_release() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+// Wait: convergent form, and one for a warp whose lanes have diverged.
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_divergent() {
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Named CTA barrier `id` over the first/any `threads` threads that call it (a multiple of 32).
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier --
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
