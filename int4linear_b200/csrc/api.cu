@@ -290,6 +290,9 @@ int host_pipelined(DeviceCtx* ctx, const void* x_h, const void* w_h, void* y_h, 
         for (int i = 0; ok && i < 8; ++i)
             ok = cudaEventCreateWithFlags(&ctx->host_ev_x[i], cudaEventDisableTiming) == cudaSuccess &&
                  cudaEventCreateWithFlags(&ctx->host_ev_y[i], cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; ok && i < 4; ++i)
+            ok = cudaEventCreateWithFlags(&ctx->host_ev_wc[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&ctx->host_ev_yc[i], cudaEventDisableTiming) == cudaSuccess;
         if (!ok) { cudaGetLastError(); ctx->host_up = nullptr; return INT4L_ERR_CUDA; }
     }
     const size_t row_x = static_cast<size_t>(k) / 2, row_y = static_cast<size_t>(n) * 4;
@@ -299,13 +302,43 @@ int host_pipelined(DeviceCtx* ctx, const void* x_h, const void* w_h, void* y_h, 
     uint8_t* xd = static_cast<uint8_t*>(ctx->stage_x);
     uint8_t* yd = static_cast<uint8_t*>(ctx->stage_y);
     bool ok = true;
-    if (!reuse_w) {
+    int rc = INT4L_OK;
+    // The download of Y is the longest leg (4 bytes per output against half a byte per operand
+    // element), so it should start as early as possible.  When W has to be uploaded too, it goes up
+    // in four column chunks behind the first row block of X, and that row block is computed chunk
+    // by chunk as they land: the first download starts after 1/8 of X and 1/4 of W instead of after
+    // all of W.  The chunk results are compact slabs in the staging area of that row block and go
+    // to their place in y_h with a strided copy.
+    int first = 0;  // row blocks already done by the chunked start
+    const int chunk_n = ((n + 3) / 4 + 255) / 256 * 256;
+    if (!reuse_w && n >= 4 * 256) {
+        const uint8_t* wh = static_cast<const uint8_t*>(w_h);
+        uint8_t* wd = static_cast<uint8_t*>(ctx->stage_w);
+        const int rows = m < block ? m : block;
+        ok = cudaMemcpyAsync(xd, xh, rows * row_x, cudaMemcpyHostToDevice, ctx->host_up) == cudaSuccess;
+        size_t slab = 0;
+        for (int j = 0, c0 = 0; ok && c0 < n; ++j, c0 += chunk_n) {
+            const int cw = n - c0 < chunk_n ? n - c0 : chunk_n;
+            ok = cudaMemcpyAsync(wd + c0 * row_x, wh + c0 * row_x, cw * row_x, cudaMemcpyHostToDevice, ctx->host_up) == cudaSuccess &&
+                 cudaEventRecord(ctx->host_ev_wc[j], ctx->host_up) == cudaSuccess &&
+                 cudaStreamWaitEvent(ctx->host_run, ctx->host_ev_wc[j], 0) == cudaSuccess;
+            if (!ok) break;
+            Problem p{xd, wd + c0 * row_x, yd + slab, rows, cw, k};
+            rc = dispatch(ctx, p, ctx->host_run);
+            if (rc != INT4L_OK) break;
+            ok = cudaEventRecord(ctx->host_ev_yc[j], ctx->host_run) == cudaSuccess &&
+                 cudaStreamWaitEvent(ctx->host_down, ctx->host_ev_yc[j], 0) == cudaSuccess &&
+                 cudaMemcpy2DAsync(yh + static_cast<size_t>(c0) * 4, row_y, yd + slab, static_cast<size_t>(cw) * 4,
+                                   static_cast<size_t>(cw) * 4, rows, cudaMemcpyDeviceToHost, ctx->host_down) == cudaSuccess;
+            slab += static_cast<size_t>(rows) * cw * 4;
+        }
+        first = 1;
+    } else if (!reuse_w) {
         ok = cudaMemcpyAsync(ctx->stage_w, w_h, static_cast<size_t>(n) * row_x, cudaMemcpyHostToDevice, ctx->host_up) == cudaSuccess &&
              cudaEventRecord(ctx->host_ev_w, ctx->host_up) == cudaSuccess &&
              cudaStreamWaitEvent(ctx->host_run, ctx->host_ev_w, 0) == cudaSuccess;
     }
-    int rc = INT4L_OK;
-    for (int i = 0, r0 = 0; ok && r0 < m; ++i, r0 += block) {
+    for (int i = first, r0 = first * block; ok && rc == INT4L_OK && r0 < m; ++i, r0 += block) {
         const int rows = m - r0 < block ? m - r0 : block;
         ok = cudaMemcpyAsync(xd + r0 * row_x, xh + r0 * row_x, rows * row_x, cudaMemcpyHostToDevice, ctx->host_up) == cudaSuccess &&
              cudaEventRecord(ctx->host_ev_x[i], ctx->host_up) == cudaSuccess &&

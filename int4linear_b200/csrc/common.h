@@ -68,6 +68,7 @@ struct DeviceCtx {
     // Streams and events of the pipelined host-buffer path (created on first use).
     cudaStream_t host_up = nullptr, host_run = nullptr, host_down = nullptr;
     cudaEvent_t host_ev_w = nullptr, host_ev_x[8] = {}, host_ev_y[8] = {};
+    cudaEvent_t host_ev_wc[4] = {}, host_ev_yc[4] = {};  // W column chunks of the first row block
     const void* stage_w_src = nullptr;  // host weights currently resident in stage_w
     size_t stage_w_src_bytes = 0;
     // Scratch of the two-pass path (expanded operands), grown on demand.

@@ -157,6 +157,16 @@ def test_host_buffer_entry_point_pipelined(cuda):
     assert L.last_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(2148, 2500, 256), (1100, 4099, 128), (4096, 1024, 128)])
+def test_host_buffer_entry_point_chunked_start(cuda, m, n, k):
+    """With weights to upload, the first row block is computed in four column chunks of W (compact
+    slabs, strided download): ragged last chunk, odd n, the smallest n that is chunked."""
+    x, w, xp, wp = make_case(m, n, k, seed=15)
+    y = L.linear_host(xp, wp, k)
+    assert O.is_same(y, O.linear_ref_sgemm(x, w))
+    assert L.last_status() == 0
+
+
 def test_host_buffer_entry_point_with_two_pass(cuda):
     """The host-buffer entry point must work when the dispatcher takes the two-pass path (it keeps
     its own staging lock while the two-pass scratch is looked up)."""
