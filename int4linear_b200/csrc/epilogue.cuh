@@ -122,4 +122,63 @@ __device__ __forceinline__ void drain_accumulator_scaled(uint32_t t_addr, int wi
     }
 }
 
+// The same dequantising epilogue through shared-memory staging and TMA stores: 64 accumulator
+// columns (two tensor-memory loads) become one 32 x 128-byte bf16 tile, written in the 128B-swizzled
+// layout and stored with one bulk copy that clips the M and N tails.  Needs n % 8 == 0 (16-byte
+// row pitch of Y).  Column scales and biases: lane l fetches those of columns l and l + 32 of the
+// NEXT chunk while the current one is converted (two coalesced loads per vector instead of a
+// dependent chain of per-column loads), and the values reach the other lanes by shuffle.
+__device__ __forceinline__ void drain_accumulator_scaled_tma(uint32_t t_addr, int width, int row0, int col0, int m, int n,
+                                                             const ScaledOut& so, const CUtensorMap* tm_y16,
+                                                             uint32_t stage0, uint32_t& chunk_no, int lane)
+{
+    const int row = row0 + lane;
+    const float rs = (so.row_scale != nullptr && row < m) ? __ldg(so.row_scale + row) : 1.0f;
+    const int n_live = (row0 < m && col0 < n) ? (min(width, n - col0) + 63) / 64 : 0;
+    float cs_next[2] = {1.0f, 1.0f}, b_next[2] = {0.0f, 0.0f};
+    auto fetch = [&](int c) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int col = min(col0 + c + 32 * hf + lane, n - 1);  // clamped: columns beyond n are clipped by the store
+            cs_next[hf] = so.col_scale != nullptr ? __ldg(so.col_scale + col) : 1.0f;
+            b_next[hf] = so.bias != nullptr ? __ldg(so.bias + col) : 0.0f;
+        }
+    };
+    if (n_live > 0) fetch(0);
+#pragma unroll 1
+    for (int i = 0; i < n_live; ++i) {
+        const int c = i * 64;
+        const float cs_cur[2] = {cs_next[0], cs_next[1]}, b_cur[2] = {b_next[0], b_next[1]};
+        if (i + 1 < n_live) fetch(c + 64);
+        uint32_t v[2][32];
+        tmem_ld_32x32(t_addr + c, v[0]);
+        tmem_ld_32x32(t_addr + c + 32, v[1]);
+        tmem_ld_wait();
+        uint32_t h[32];  // 64 bf16 values, two per register
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int hf = j >> 4, l0 = (2 * j) & 31;
+            const float s0 = __shfl_sync(0xffffffffu, cs_cur[hf], l0), s1 = __shfl_sync(0xffffffffu, cs_cur[hf], l0 + 1);
+            const float o0 = __shfl_sync(0xffffffffu, b_cur[hf], l0), o1 = __shfl_sync(0xffffffffu, b_cur[hf], l0 + 1);
+            const float f0 = fmaf(static_cast<float>(static_cast<int>(v[hf][l0]) >> 8) * rs, s0, o0);
+            const float f1 = fmaf(static_cast<float>(static_cast<int>(v[hf][l0 + 1]) >> 8) * rs, s1, o1);
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(f0, f1);
+            h[j] = *reinterpret_cast<const uint32_t*>(&pr);
+        }
+        const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            sts128(stg + lane * 128 + ((q ^ (lane & 7)) << 4), make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(tm_y16, stg, col0 + c, row0);
+            tma_store_commit();
+        }
+        ++chunk_no;
+    }
+}
+
 }  // namespace i4l

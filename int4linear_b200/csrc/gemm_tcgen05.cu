@@ -289,9 +289,11 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
-            if (!kTmaStore && so.y16 != nullptr)
-                drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
-            else
+            if (so.y16 != nullptr) {
+                // Dequantised bf16 output; y_maps[0] then describes the bf16 matrix.
+                if constexpr (kTmaStore) drain_accumulator_scaled_tma(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
+                else drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
+            } else
                 drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
             tc_fence_before_sync();
             __syncwarp();
@@ -456,7 +458,10 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     else
         rc = make_tensor_map_2d(ctx, &tm_w, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW, false);
     if (rc != INT4L_OK) return rc;
-    if (kTmaStore && gather == nullptr) {
+    if (kTmaStore && p.scaled.y16 != nullptr) {
+        rc = make_tensor_map_2d(ctx, &tm_y, p.scaled.y16, 2, p.n, p.m, static_cast<uint64_t>(p.n) * 2, 64, 32, true);
+        if (rc != INT4L_OK) return rc;
+    } else if (kTmaStore && gather == nullptr) {
         rc = make_tensor_map_2d(ctx, &tm_y, p.y, 4, p.n, p.m, static_cast<uint64_t>(p.n) * 4, 32, 32, true);
         if (rc != INT4L_OK) return rc;
     } else {
@@ -568,7 +573,11 @@ int setup_tcgen05(DeviceCtx* ctx)
 // machine leaves SMs idle.
 int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
-    const bool tma_store = (p.n % 4 == 0) && !getenv_flag_direct_store() && p.scaled.y16 == nullptr;
+    auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    const bool tma_store = !getenv_flag_direct_store() &&
+                           (p.scaled.y16 == nullptr
+                                ? p.n % 4 == 0
+                                : (p.n % 8 == 0 && aligned16(p.scaled.y16)));
     if (p.w_expanded) {
         // Pre-expanded weights: CTA pairs whenever there is more than one row block, else one CTA.
         if (p.m > 128)

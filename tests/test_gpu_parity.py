@@ -274,7 +274,7 @@ def test_prepared_weights_path(cuda, shape, direct):
     assert O.is_same(yb.cpu().numpy(), ref + bias[None, :])
 
 
-@pytest.mark.parametrize("shape", [(300, 520, 256), (1024, 1024, 512), (64, 72, 96), (257, 130, 1056), (4096, 4096, 1024)],
+@pytest.mark.parametrize("shape", [(300, 520, 256), (1024, 1024, 512), (64, 72, 96), (257, 130, 1056), (4096, 4096, 1024), (515, 1096, 128)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_scaled_bf16_epilogue(cuda, shape):
     """Dequantising epilogue: bf16(float(acc) * row_scale * col_scale + bias).  The integer part is
@@ -301,6 +301,17 @@ def test_scaled_bf16_epilogue(cuda, shape):
     # unscaled: bf16 of the exact integers (all |acc| here are exactly representable up to rounding)
     exact = torch.from_numpy(acc).to(torch.bfloat16).float().numpy()
     assert np.array_equal(got, exact)
+    # The per-thread-store epilogue (forced here; taken by itself when n % 8 != 0) and the
+    # TMA-store one do the same arithmetic, so their results must be identical.
+    full = [torch.from_numpy(v).to(cuda) for v in (rs, cs, b)]
+    y_tma = L.linear_scaled(xd, wd, *full)
+    L.set_tuning(0, True, -1)
+    try:
+        y_direct = L.linear_scaled(xd, wd, *full)
+        torch.cuda.synchronize()
+    finally:
+        L.set_tuning(0, False, -1)
+    assert torch.equal(y_tma, y_direct)
 
 
 def test_bounded_wait_reports_and_recovers(cuda):
