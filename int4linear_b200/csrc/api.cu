@@ -655,3 +655,20 @@ void linear_v21_launch(void* x_packed_d, void* w_packed_d, void* y_d, int m, int
 {
     int4_linear_launch(x_packed_d, w_packed_d, y_d, m, n, k);
 }
+
+// The launchers of the reference's earlier kernel generations (kernels/linear_v0.h:168,
+// linear_v1.h:208, linear_v2.h:284, and the same declaration at the end of linear_v10.h,
+// linear_v11.h and linear_v20.h) have the same signature and contract; call sites written against
+// any of them get the same sm_100a kernels.
+#define I4L_LEGACY_LAUNCHER(name)                                                              \
+    void name(void* x_packed_d, void* w_packed_d, void* y_d, int m, int n, int k)                \
+    {                                                                                          \
+        int4_linear_launch(x_packed_d, w_packed_d, y_d, m, n, k);                              \
+    }
+I4L_LEGACY_LAUNCHER(linear_v0_launch)
+I4L_LEGACY_LAUNCHER(linear_v1_launch)
+I4L_LEGACY_LAUNCHER(linear_v2_launch)
+I4L_LEGACY_LAUNCHER(linear_v10_launch)
+I4L_LEGACY_LAUNCHER(linear_v11_launch)
+I4L_LEGACY_LAUNCHER(linear_v20_launch)
+#undef I4L_LEGACY_LAUNCHER

@@ -50,3 +50,27 @@ def test_reference_gpu_kernel_agrees(cuda):
     want = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
     assert O.is_same(y_ref_gpu.cpu().numpy(), want)
     assert O.is_same(y_ours.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("version", [0, 1, 2, 10, 11, 20, 21])
+def test_launcher_of_every_reference_generation(cuda, version):
+    """Every linear_vN_launch symbol (C++ linkage, as the reference declares them) computes the
+    operator: called through its mangled name with device pointers."""
+    import ctypes
+    import numpy as np
+    import torch
+    from int4linear_b200 import _lib
+    from conftest import make_case
+    from oracle import oracle as O
+    lib = _lib.load()
+    name = f"linear_v{version}_launch"
+    fn = getattr(lib, f"_Z{len(name)}{name}PvS_S_iii")
+    fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3
+    fn.restype = None
+    m, n, k = 200, 264, 160
+    x, w, xp, wp = make_case(m, n, k, seed=70 + version)
+    xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+    yd = torch.empty((m, n), dtype=torch.int32, device=cuda)
+    fn(xd.data_ptr(), wd.data_ptr(), yd.data_ptr(), m, n, k)  # blocking, like the reference
+    assert lib.int4_linear_last_status() == 0
+    assert O.is_same(yd.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))

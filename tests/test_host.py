@@ -58,6 +58,18 @@ def test_library_exports_every_declared_symbol():
     assert lib.int4_linear_version() >= 100
 
 
+def test_library_exports_the_launchers_of_every_reference_generation():
+    """kernels/linear_vN.h of the reference declare `void linear_vN_launch(void*, void*, void*, int,
+    int, int)` with C++ linkage for N in {0, 1, 2, 10, 11, 20, 21}; the library exports all of them
+    and the compat directory has a header of each name."""
+    lib = _lib.load()
+    for v in (0, 1, 2, 10, 11, 20, 21):
+        name = f"linear_v{v}_launch"
+        assert hasattr(lib, f"_Z{len(name)}{name}PvS_S_iii"), name
+        hdr = os.path.join(ROOT, "int4linear_b200", "compat", "kernels", f"linear_v{v}.h")
+        assert name in open(hdr).read()
+
+
 def test_argument_checks_need_no_gpu():
     lib = _lib.load()
     buf = np.zeros(4096, dtype=np.uint8)
