@@ -596,9 +596,11 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
                                   ? 1.0
                                   : static_cast<double>((2 * pair_tiles + ctx->max_pairs - 1) / ctx->max_pairs) / 2.0;
     const double cost_pairs = p.m > 128 ? pair_waves * 1.0 : 1e30;  // a lone row block would leave CTA 1 idle
-    const double cost256 = whole_waves(tiles(256), ctx->sm_count) * 1.25;
-    const double cost128 = whole_waves(tiles(128), ctx->sm_count) * 0.90;
-    const double cost64 = whole_waves(tiles(64), ctx->sm_count) * 0.72;
+    // Tile times relative to the pair tile, from CUDA-graph replays (no launch overhead in the
+    // figures) at K = 1024 and 4096: 128 x 256 on one CTA 1.7, 128 x 128 1.1, 128 x 64 0.9.
+    const double cost256 = whole_waves(tiles(256), ctx->sm_count) * 1.7;
+    const double cost128 = whole_waves(tiles(128), ctx->sm_count) * 1.1;
+    const double cost64 = whole_waves(tiles(64), ctx->sm_count) * 0.9;
     int bn = 256;
     double best = cost256;
     if (cost128 < best) { best = cost128; bn = 128; }

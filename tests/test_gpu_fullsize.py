@@ -1,4 +1,4 @@
-"""GPU: the BASELINE configurations at full size.
+"""GPU: the five benchmark configurations and the headline shape at full size.
 
 The CPU oracle's triple loop cannot cover these in seconds, so each shape is
 checked (a) exactly on a sample of rows computed by the oracle, (b) exactly
