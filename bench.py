@@ -366,7 +366,10 @@ def main():
             step(i)
         b1.record()
         barrier()
-        back_to_back = b0.elapsed_time(b1) / args.steps
+        bt = torch.tensor([b0.elapsed_time(b1) / args.steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(bt, op=dist.ReduceOp.MAX)  # every rank takes part; max over ranks
+        back_to_back = float(bt.item())
     # Microsecond-scale tensor shapes (c1): one launch is comparable with the launch overhead an
     # event pair sees, so the K launches are also timed as one CUDA-graph replay over rotating
     # copies of X, W and Y that together exceed L2.
@@ -531,10 +534,7 @@ def main():
     if graph_replay is not None:
         line["graph_replay"] = graph_replay
     if back_to_back is not None:
-        b = torch.tensor([back_to_back], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(b, op=dist.ReduceOp.MAX)
-        line["back_to_back"] = {"ms_per_step": float(b.item()), "value": ops / (float(b.item()) * 1e-3) / 1e12,
+        line["back_to_back"] = {"ms_per_step": back_to_back, "value": ops / (back_to_back * 1e-3) / 1e12,
                                 "unit": "TOPS", "note": "same launches without the L2 flush between them; working set > 2 x L2"}
     if gather_ms is not None:
         line["all_gather_ms"] = gather_ms
