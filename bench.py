@@ -316,6 +316,7 @@ def main():
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
     pipelined = None
+    step_ms = None
     if rotate:
         # A single ~5 us launch is below what an event pair (or a Python call) resolves, so the K
         # steps are captured into one CUDA graph -- K launches, each on its own copy of W -- and
@@ -346,13 +347,21 @@ def main():
         pipelined = {f"overlap_{mode}": graph_ms(mode) / args.steps for mode in (1, 2)}
         launches0 = L.launch_count() - args.steps  # the timed replay ran the K captured launches
     else:
+        # Three more untimed steps queued directly in front of the timed ones: the host work between
+        # the warm-up and here (barrier, sampler thread) leaves the GPU idle long enough to drop its
+        # clocks, and the first timed launch would otherwise pay for the ramp.
+        for i in range(3):
+            flush.zero_()
+            step(i)
+        launches0 = L.launch_count()
         for i in range(args.steps):
             flush.zero_()  # evict operands and result from L2 (test/benchmark.cu:93-96)
             starts[i].record()
             step(i)
             ends[i].record()
         barrier()
-        total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+        step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+        total_ms = sum(step_ms)
     launches = L.launch_count() - launches0
     # Second figure for the tensor-bound shapes: the same K launches back to back, no flush between
     # them (meaningful only where operands + result exceed L2, as the layers of a model would run).
@@ -531,6 +540,8 @@ def main():
                                      "by preceding work, 2 = weights and X; `value` uses ordinary launches")
     if e2e is not None:
         line["e2e"] = e2e
+    if step_ms is not None:
+        line["step_ms"] = {"min": min(step_ms), "median": statistics.median(step_ms), "max": max(step_ms)}  # rank 0
     if graph_replay is not None:
         line["graph_replay"] = graph_replay
     if back_to_back is not None:
