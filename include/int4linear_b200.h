@@ -85,8 +85,9 @@ int int4_linear_bias_launch_async(const void* x_packed_d, const void* w_packed_d
  * are device pointers, each may be NULL (factor 1 / addend 0); y_bf16_d is m x n bfloat16,
  * row-major, 16-byte aligned.  The integer sum is exact, its conversion to float is exact, the
  * scaling is one float multiply and one fused multiply-add, the result is rounded to nearest
- * even.  Halves the bytes of Y, the dominant stream of large shapes.  Always runs on the
- * tensor-memory kernel family.  No reference counterpart (its output is int32 only).
+ * even.  Halves the bytes of Y, the dominant stream of large shapes.  Runs on the tensor-memory
+ * kernels and, for decode shapes, on the streaming kernels (same bits from both); the legacy path
+ * has no such epilogue.  No reference counterpart (its output is int32 only).
  */
 int int4_linear_scaled_launch_async(const void* x_packed_d, const void* w_packed_d, const float* row_scale_d,
                                     const float* col_scale_d, const float* bias_d, void* y_bf16_d,

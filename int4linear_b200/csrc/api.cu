@@ -447,7 +447,9 @@ int int4_linear_scaled_launch_async(const void* x, const void* w, const float* r
     p.scaled.col_scale = col_scale_d;
     p.scaled.bias = bias_d;
     p.scaled.y16 = y_bf16_d;
-    rc = launch_tcgen05(ctx, p, static_cast<cudaStream_t>(stream));
+    // Decode shapes keep their streaming kernels; the legacy path has no scaled epilogue.
+    rc = choose_path(ctx, p) == INT4L_PATH_SKINNY ? launch_skinny(ctx, p, static_cast<cudaStream_t>(stream))
+                                                  : launch_tcgen05(ctx, p, static_cast<cudaStream_t>(stream));
     t_last_status = rc;
     return rc;
 }

@@ -25,6 +25,8 @@
 // (which runs them as 256 x 128 tiles that are almost entirely padding).
 #include <cstdlib>
 
+#include <cuda_bf16.h>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -51,11 +53,28 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Final write of one output: the exact int32 (plus optional int32 bias), or the dequantised
+// bfloat16 with the same arithmetic as the tensor-memory kernels' epilogue.
+__device__ __forceinline__ void write_out(int* __restrict__ y, const int* __restrict__ bias, const ScaledOut& so,
+                                          int r, int col, int n, int acc)
+{
+    if (so.y16 != nullptr) {
+        const float rs = so.row_scale != nullptr ? __ldg(so.row_scale + r) : 1.0f;
+        const float cs = so.col_scale != nullptr ? __ldg(so.col_scale + col) : 1.0f;
+        const float b = so.bias != nullptr ? __ldg(so.bias + col) : 0.0f;
+        static_cast<__nv_bfloat16*>(so.y16)[static_cast<size_t>(r) * n + col] =
+            __float2bfloat16_rn(fmaf(static_cast<float>(acc) * rs, cs, b));
+    } else {
+        y[static_cast<size_t>(r) * n + col] = acc + (bias ? __ldg(bias + col) : 0);
+    }
+}
+
 // MB = number of 16-row blocks of X (m <= 16 * MB).
 template <int MB>
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
-                      int m, int n, int k, int groups_total, int groups_per_cta_max, int x_pitch, const int* __restrict__ bias)
+                      int m, int n, int k, int groups_total, int groups_per_cta_max, int x_pitch, const int* __restrict__ bias,
+                      const ScaledOut so)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* xs = smem;                                                  // [MB*16][x_pitch]
@@ -156,7 +175,7 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
     for (int i = tid; i < m * cols; i += kSkinnyThreads) {
         const int r = i / cols, cc = i - r * cols;
         const int col = col_base + cc;
-        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * MB * 16 + r) * 8 + (cc & 7)] + (bias ? __ldg(bias + col) : 0);
+        if (col < n) write_out(y, bias, so, r, col, n, acc[((cc >> 3) * MB * 16 + r) * 8 + (cc & 7)]);
     }
 }
 
@@ -171,7 +190,8 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
 template <int KBW, int D, int MINB>
 __global__ void __launch_bounds__(kSkinnyThreads, MINB)
 gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
-                          int m, int n, int k, int groups_total, int overlap, const int* __restrict__ bias)
+                          int m, int n, int k, int groups_total, int overlap, const int* __restrict__ bias,
+                          const ScaledOut so)
 {
     // D = groups of weight loads in flight per warp.
     // overlap: 0 = ordinary launch.  1, 2 = launched with programmatic stream serialisation:
@@ -264,7 +284,7 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
     for (int i = tid; i < m * cols; i += kSkinnyThreads) {
         const int r = i / cols, cc = i - r * cols;
         const int col = col_base + cc;
-        if (col < n) y[static_cast<size_t>(r) * n + col] = acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)] + (bias ? __ldg(bias + col) : 0);
+        if (col < n) write_out(y, bias, so, r, col, n, acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)]);
     }
 }
 
@@ -488,16 +508,16 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         cfg.numAttrs = overlap ? 1 : 0;
         cudaError_t e;
         if (kb_count <= 16)
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<1, 4, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<1, 4, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias, p.scaled);
         else if (kb_count <= 32)
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<2, 2, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<2, 2, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias, p.scaled);
         else
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<4, 2, 1>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias);
+            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<4, 2, 1>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias, p.scaled);
         count_launch();
         if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
         return INT4L_OK;
     }
-    if (p.m <= 16 && p.k >= 256 && skinny_variant() != 2) {
+    if (p.m <= 16 && p.k >= 256 && skinny_variant() != 2 && p.scaled.y16 == nullptr) {
         // Whole slab resident when it fits (one buffer per warp holding every row of the CTA's
         // run for the warp's slice), otherwise two 48-row buffers per warp.
         const int rows_max = s.groups_per_cta_max * 8;
@@ -526,11 +546,11 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         }
     }
     if (s.mb == 1)
-        gemm_s4_skinny_kernel<1><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias);
+        gemm_s4_skinny_kernel<1><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias, p.scaled);
     else if (s.mb == 2)
-        gemm_s4_skinny_kernel<2><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias);
+        gemm_s4_skinny_kernel<2><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias, p.scaled);
     else
-        gemm_s4_skinny_kernel<4><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias);
+        gemm_s4_skinny_kernel<4><<<s.grid, kSkinnyThreads, s.smem, stream>>>(x, w, y, p.m, p.n, p.k, s.groups_total, s.groups_per_cta_max, s.x_pitch, p.bias, p.scaled);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }

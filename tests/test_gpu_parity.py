@@ -274,7 +274,9 @@ def test_prepared_weights_path(cuda, shape, direct):
     assert O.is_same(yb.cpu().numpy(), ref + bias[None, :])
 
 
-@pytest.mark.parametrize("shape", [(300, 520, 256), (1024, 1024, 512), (64, 72, 96), (257, 130, 1056), (4096, 4096, 1024), (515, 1096, 128)],
+@pytest.mark.parametrize("shape", [(300, 520, 256), (1024, 1024, 512), (64, 72, 96), (257, 130, 1056), (4096, 4096, 1024), (515, 1096, 128),
+                                   # decode shapes: the streaming kernels write the scaled output themselves
+                                   (16, 1024, 4096), (8, 264, 2048), (16, 512, 8192), (32, 520, 256), (5, 77, 96)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_scaled_bf16_epilogue(cuda, shape):
     """Dequantising epilogue: bf16(float(acc) * row_scale * col_scale + bias).  The integer part is
@@ -312,6 +314,15 @@ def test_scaled_bf16_epilogue(cuda, shape):
     finally:
         L.set_tuning(0, False, -1)
     assert torch.equal(y_tma, y_direct)
+    # Whatever kernel family the dispatcher picks (decode shapes go to the streaming kernels), the
+    # tensor-memory family must give the same bits.
+    L.set_path(L.PATH_TCGEN05)
+    try:
+        y_tc = L.linear_scaled(xd, wd, *full)
+        torch.cuda.synchronize()
+    finally:
+        L.set_path(L.PATH_AUTO)
+    assert torch.equal(y_tma, y_tc)
 
 
 def test_bounded_wait_reports_and_recovers(cuda):
