@@ -17,6 +17,8 @@ def test_ops_are_registered_with_shape_inference():
     assert p.shape == (3, 3) and p.dtype == torch.int32
     with pytest.raises(Exception):
         torch.ops.int4linear.linear(x, torch.empty((9, 32), dtype=torch.uint8, device="meta"))
+    z = torch.ops.int4linear.linear_scaled(x, w, None, torch.empty(9, device="meta"), None)
+    assert z.shape == (5, 9) and z.dtype == torch.bfloat16
 
 
 def test_no_cpu_kernel():
@@ -35,3 +37,20 @@ def test_op_matches_oracle(cuda):
     y = torch.ops.int4linear.linear(xp, wp)
     torch.cuda.synchronize()
     assert O.is_same(y.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))
+
+
+@pytest.mark.gpu
+def test_scaled_op_matches_the_integer_op(cuda):
+    """linear_scaled = the integer result of the same operands, scaled in float32 and rounded to bf16."""
+    m, n, k = 48, 264, 512
+    xp = torch.from_numpy(L.uniform_s4_packed(21, m, k)).to(cuda)
+    wp = torch.from_numpy(L.uniform_s4_packed(22, n, k)).to(cuda)
+    rs = torch.rand(m, device=cuda) * 0.1 + 0.01
+    cs = torch.rand(n, device=cuda) * 0.1 + 0.01
+    b = torch.randn(n, device=cuda)
+    acc = torch.ops.int4linear.linear(xp, wp).float()
+    z = torch.ops.int4linear.linear_scaled(xp, wp, rs, cs, b)
+    ref = torch.addcmul(b[None, :].expand(m, n), acc * rs[:, None], cs[None, :].expand(m, n))
+    torch.cuda.synchronize()
+    err = (z.float() - ref).abs()
+    assert bool((err <= ref.abs() * 2.0 ** -7 + 1e-6).all())  # one bf16 unit in the last place
