@@ -87,6 +87,25 @@ def test_argument_checks_need_no_gpu():
     assert lib.int4_linear_set_tuning(0, 0, -1) == 0
 
 
+def test_gather_entry_point_argument_checks_need_no_gpu():
+    import ctypes
+    lib = _lib.load()
+    base = 1 << 20
+    ptrs = (ctypes.c_void_p * 2)(base, base + 4096)
+    ok = (base, base, None, ptrs)
+    assert lib.int4_linear_launch_gather_async(base, base, None, None, 2, 0, 8, 32, 64, 32, None) == 1   # no destinations
+    assert lib.int4_linear_launch_gather_async(*ok, 9, 0, 8, 32, 64, 32, None) == 1                      # world > 8
+    assert lib.int4_linear_launch_gather_async(*ok, 2, -32, 8, 32, 64, 32, None) == 1                    # negative offset
+    bad = (ctypes.c_void_p * 2)(base, base + 4)
+    assert lib.int4_linear_launch_gather_async(base, base, None, bad, 2, 0, 8, 32, 64, 32, None) == 1    # misaligned destination
+    assert lib.int4_linear_launch_gather_async(*ok, 2, 0, 8, 32, 64, 48, None) == 2                      # k % 32 != 0
+    import torch
+    from int4linear_b200.linear import linear_gather
+    x = torch.zeros((8, 16), dtype=torch.uint8)
+    with pytest.raises(ValueError):
+        linear_gather(x, x, [base], 0, 8)   # CPU tensors: there is no CPU implementation
+
+
 def test_no_gpu_means_error_not_fallback():
     import torch
     if torch.cuda.is_available():
