@@ -27,8 +27,10 @@
 //                 of two TMEM accumulator buffers; tcgen05.commit releases the
 //                 unpacked slot / publishes the finished accumulator.
 //     warps 2-5   epilogue: tcgen05.ld the accumulator (one TMEM sub-partition of
-//                 32 lanes each), undo the scaling, write Y.  Overlaps the next
-//                 tile's main loop through the second accumulator buffer.
+//                 32 lanes each), undo the scaling, write Y (int32 through staged TMA
+//                 stores -- to one matrix, or to every rank's copy when the result is
+//                 gathered -- or dequantised bf16).  Overlaps the next tile's main
+//                 loop through the second accumulator buffer.
 //
 // The unpack
 //   A packed 32-bit word x holds nibbles e0..e7.  (x << 4) & 0xF0F0F0F0 is four
