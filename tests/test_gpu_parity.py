@@ -344,3 +344,22 @@ def test_bounded_wait_reports_and_recovers(cuda):
     torch.cuda.synchronize()
     assert lib.int4_linear_last_status() == 0       # ... once; the device is still usable
     assert O.is_same(y.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))
+
+
+def test_random_shapes_through_the_dispatcher(cuda):
+    """Seeded random shapes through the automatic path/tile choice (pairs, the three single-CTA
+    tile widths, tail splitting, the decode kernels, TMA and per-thread stores), each bit-exact
+    against the oracle."""
+    rng = np.random.default_rng(20240607)
+    shapes = []
+    for _ in range(48):
+        m = int(rng.choice([rng.integers(1, 40), rng.integers(40, 300), rng.integers(300, 1400)]))
+        n = int(rng.choice([rng.integers(1, 64), rng.integers(64, 600), rng.integers(600, 2600)]))
+        k = 32 * int(rng.integers(1, 48))
+        shapes.append((m, n, k))
+    for i, (m, n, k) in enumerate(shapes):
+        x, w, xp, wp = make_case(m, n, k, seed=200 + i)
+        y = run_device(cuda, xp, wp, k)
+        ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+        assert O.is_same(y, ref), (m, n, k)
+    assert L.last_status() == 0
