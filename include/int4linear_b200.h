@@ -94,6 +94,14 @@ int int4_linear_scaled_launch_async(const void* x_packed_d, const void* w_packed
                                     int m, int n, int k, void* stream);
 
 /*
+ * The same with IEEE half-precision output (y_f16_d: m x n halves).  The scaled value must fit the
+ * half range (|v| < 65504), else it rounds to infinity as the conversion instruction does.
+ */
+int int4_linear_scaled_f16_launch_async(const void* x_packed_d, const void* w_packed_d, const float* row_scale_d,
+                                    const float* col_scale_d, const float* bias_d, void* y_f16_d,
+                                    int m, int n, int k, void* stream);
+
+/*
  * N-sharded GEMM fused with the all-gather of its result.  This rank holds n_local rows of W
  * (columns [col_offset, col_offset + n_local) of the full Y) and the full X; y_full_ptrs is a HOST
  * array of `world` (<= 8) device pointers to the m x n_total int32 result buffer of every rank

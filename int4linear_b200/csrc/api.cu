@@ -435,23 +435,36 @@ int int4_linear_launch_prepared_async(const void* x, const void* w_expanded_d, c
     return rc;
 }
 
-int int4_linear_scaled_launch_async(const void* x, const void* w, const float* row_scale_d, const float* col_scale_d,
-                                    const float* bias_d, void* y_bf16_d, int m, int n, int k, void* stream)
+static int scaled_launch(const void* x, const void* w, const float* row_scale_d, const float* col_scale_d,
+                         const float* bias_d, void* y16_d, int fp16, int m, int n, int k, void* stream)
 {
-    int rc = check_args(x, w, y_bf16_d, m, n, k);
+    int rc = check_args(x, w, y16_d, m, n, k);
     if (rc != INT4L_OK) { t_last_status = rc; return rc; }
     DeviceCtx* ctx = current_ctx(&rc);
     if (!ctx) { t_last_status = rc; return rc; }
-    Problem p{x, w, y_bf16_d, m, n, k};
+    Problem p{x, w, y16_d, m, n, k};
     p.scaled.row_scale = row_scale_d;
     p.scaled.col_scale = col_scale_d;
     p.scaled.bias = bias_d;
-    p.scaled.y16 = y_bf16_d;
+    p.scaled.y16 = y16_d;
+    p.scaled.fp16 = fp16;
     // Decode shapes keep their streaming kernels; the legacy path has no scaled epilogue.
     rc = choose_path(ctx, p) == INT4L_PATH_SKINNY ? launch_skinny(ctx, p, static_cast<cudaStream_t>(stream))
                                                   : launch_tcgen05(ctx, p, static_cast<cudaStream_t>(stream));
     t_last_status = rc;
     return rc;
+}
+
+int int4_linear_scaled_launch_async(const void* x, const void* w, const float* row_scale_d, const float* col_scale_d,
+                                    const float* bias_d, void* y_bf16_d, int m, int n, int k, void* stream)
+{
+    return scaled_launch(x, w, row_scale_d, col_scale_d, bias_d, y_bf16_d, 0, m, n, k, stream);
+}
+
+int int4_linear_scaled_f16_launch_async(const void* x, const void* w, const float* row_scale_d, const float* col_scale_d,
+                                        const float* bias_d, void* y_f16_d, int m, int n, int k, void* stream)
+{
+    return scaled_launch(x, w, row_scale_d, col_scale_d, bias_d, y_f16_d, 1, m, n, k, stream);
 }
 
 int int4_linear_launch_gather_async(const void* x, const void* w_shard, const int* bias_d, void* const* y_full_ptrs,

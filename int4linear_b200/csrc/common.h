@@ -2,6 +2,8 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -13,15 +15,24 @@ namespace i4l {
 // reference's (kernels/linear_v21.h:62-69): X is M x K and W is N x K, both
 // packed two signed nibbles per byte (low nibble = even index) with a row
 // pitch of K/2 bytes; Y is M x N int32, row-major.
-// Optional scaled bfloat16 output: Y16[i][j] = bf16(float(acc[i][j]) * row_scale[i] * col_scale[j] + bias[j]),
+// Optional scaled 16-bit float output: Y16[i][j] = f16(float(acc[i][j]) * row_scale[i] * col_scale[j] + bias[j]),
 // any of the three vectors may be null (factor 1 / addend 0).  Active when y16 is set; the int32 Y is
 // then not written.
 struct ScaledOut {
     const float* row_scale = nullptr;  // m per-row (per-token) factors
     const float* col_scale = nullptr;  // n per-column (per-channel) factors
     const float* bias = nullptr;       // n addends
-    void* y16 = nullptr;               // m x n bfloat16, row-major
+    void* y16 = nullptr;               // m x n 16-bit floats, row-major
+    int fp16 = 0;                      // 0: bfloat16, 1: IEEE half
 };
+
+#ifdef __CUDACC__
+// The 16-bit pattern of a scaled output value in the chosen format (round to nearest even).
+__device__ __forceinline__ unsigned short scaled_to_bits(float v, int fp16)
+{
+    return fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+#endif
 
 struct Problem {
     const void* x;

@@ -82,7 +82,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
 }
 
 // Dequantising variant: float(acc) * row_scale[row] * col_scale[col] + bias[col], rounded to
-// bfloat16 (round to nearest even), written with per-thread 16-byte stores (8 values) where the
+// bfloat16 or half (round to nearest even), written with per-thread 16-byte stores (8 values) where the
 // row pitch allows.  The int32 -> float conversion is exact (|acc| <= 64 K < 2^24).
 __device__ __forceinline__ void drain_accumulator_scaled(uint32_t t_addr, int width, int row0, int col0, int m, int n,
                                                          const ScaledOut& so, int lane)
@@ -90,7 +90,7 @@ __device__ __forceinline__ void drain_accumulator_scaled(uint32_t t_addr, int wi
     const int row = row0 + lane;
     const bool vec_ok = (n & 7) == 0;
     const float rs = (so.row_scale != nullptr && row < m) ? __ldg(so.row_scale + row) : 1.0f;
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(so.y16);
+    unsigned short* out = static_cast<unsigned short*>(so.y16);  // bfloat16 or half bit patterns
 #pragma unroll 1
     for (int c = 0; c < width; c += 32) {
         if (col0 + c >= n) break;
@@ -98,16 +98,16 @@ __device__ __forceinline__ void drain_accumulator_scaled(uint32_t t_addr, int wi
         tmem_ld_32x32(t_addr + c, v);
         tmem_ld_wait();
         if (row >= m) continue;
-        __align__(16) __nv_bfloat16 h[32];
+        __align__(16) unsigned short h[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             const int col = col0 + c + i;
             const float cs = (so.col_scale != nullptr && col < n) ? __ldg(so.col_scale + col) : 1.0f;
             const float b = (so.bias != nullptr && col < n) ? __ldg(so.bias + col) : 0.0f;
             const float f = static_cast<float>(static_cast<int>(v[i]) >> 8);
-            h[i] = __float2bfloat16_rn(fmaf(f * rs, cs, b));
+            h[i] = scaled_to_bits(fmaf(f * rs, cs, b), so.fp16);
         }
-        __nv_bfloat16* dst = out + static_cast<size_t>(row) * n + col0 + c;
+        unsigned short* dst = out + static_cast<size_t>(row) * n + col0 + c;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int col = col0 + c + 8 * q;
@@ -154,7 +154,7 @@ __device__ __forceinline__ void drain_accumulator_scaled_tma(uint32_t t_addr, in
         tmem_ld_32x32(t_addr + c, v[0]);
         tmem_ld_32x32(t_addr + c + 32, v[1]);
         tmem_ld_wait();
-        uint32_t h[32];  // 64 bf16 values, two per register
+        uint32_t h[32];  // 64 16-bit values, two per register
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
             const int hf = j >> 4, l0 = (2 * j) & 31;
@@ -162,8 +162,7 @@ __device__ __forceinline__ void drain_accumulator_scaled_tma(uint32_t t_addr, in
             const float o0 = __shfl_sync(0xffffffffu, b_cur[hf], l0), o1 = __shfl_sync(0xffffffffu, b_cur[hf], l0 + 1);
             const float f0 = fmaf(static_cast<float>(static_cast<int>(v[hf][l0]) >> 8) * rs, s0, o0);
             const float f1 = fmaf(static_cast<float>(static_cast<int>(v[hf][l0 + 1]) >> 8) * rs, s1, o1);
-            const __nv_bfloat162 pr = __floats2bfloat162_rn(f0, f1);
-            h[j] = *reinterpret_cast<const uint32_t*>(&pr);
+            h[j] = static_cast<uint32_t>(scaled_to_bits(f0, so.fp16)) | (static_cast<uint32_t>(scaled_to_bits(f1, so.fp16)) << 16);
         }
         const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
         if (lane == 0) tma_store_wait_read<1>();

@@ -62,8 +62,8 @@ __device__ __forceinline__ void write_out(int* __restrict__ y, const int* __rest
         const float rs = so.row_scale != nullptr ? __ldg(so.row_scale + r) : 1.0f;
         const float cs = so.col_scale != nullptr ? __ldg(so.col_scale + col) : 1.0f;
         const float b = so.bias != nullptr ? __ldg(so.bias + col) : 0.0f;
-        static_cast<__nv_bfloat16*>(so.y16)[static_cast<size_t>(r) * n + col] =
-            __float2bfloat16_rn(fmaf(static_cast<float>(acc) * rs, cs, b));
+        static_cast<unsigned short*>(so.y16)[static_cast<size_t>(r) * n + col] =
+            scaled_to_bits(fmaf(static_cast<float>(acc) * rs, cs, b), so.fp16);
     } else {
         y[static_cast<size_t>(r) * n + col] = acc + (bias ? __ldg(bias + col) : 0);
     }

@@ -133,9 +133,10 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias
     return out
 
 
-def linear_scaled(x_packed, w_packed, row_scale=None, col_scale=None, bias=None, out=None, stream=None):
-    """bf16 Y = (X @ W^T) * row_scale[:, None] * col_scale[None, :] + bias (see
-    int4_linear_scaled_launch_async).  Scales and bias are CUDA float32 vectors or None."""
+def linear_scaled(x_packed, w_packed, row_scale=None, col_scale=None, bias=None, out=None, stream=None, dtype=None):
+    """16-bit Y = (X @ W^T) * row_scale[:, None] * col_scale[None, :] + bias (see
+    int4_linear_scaled_launch_async).  Scales and bias are CUDA float32 vectors or None; `dtype` is
+    torch.bfloat16 (default) or torch.float16 (taken from `out` when that is given)."""
     import torch
     xb = x_packed.contiguous().view(torch.uint8)
     wb = w_packed.contiguous().view(torch.uint8)
@@ -146,12 +147,15 @@ def linear_scaled(x_packed, w_packed, row_scale=None, col_scale=None, bias=None,
         if t is not None and (t.dtype != torch.float32 or t.numel() != length or not t.is_cuda or not t.is_contiguous()):
             raise ValueError(f"{name} must be a contiguous CUDA float32 tensor with {length} elements")
     if out is None:
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=xb.device)
+        out = torch.empty((m, n), dtype=dtype or torch.bfloat16, device=xb.device)
+    if out.dtype not in (torch.bfloat16, torch.float16) or (dtype is not None and out.dtype != dtype):
+        raise ValueError("the scaled output is bfloat16 or float16")
     handle = (stream or torch.cuda.current_stream()).cuda_stream
     ptr = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+    lib = _lib.load()
+    fn = lib.int4_linear_scaled_f16_launch_async if out.dtype == torch.float16 else lib.int4_linear_scaled_launch_async
     with torch.cuda.device(xb.device):
-        st = _lib.load().int4_linear_scaled_launch_async(xb.data_ptr(), wb.data_ptr(), ptr(row_scale), ptr(col_scale),
-                                                         ptr(bias), out.data_ptr(), m, n, k, handle)
+        st = fn(xb.data_ptr(), wb.data_ptr(), ptr(row_scale), ptr(col_scale), ptr(bias), out.data_ptr(), m, n, k, handle)
     if st != 0:
         raise Int4LinearError(st, "int4_linear_scaled_launch_async")
     return out

@@ -323,6 +323,13 @@ def test_scaled_bf16_epilogue(cuda, shape):
     finally:
         L.set_path(L.PATH_AUTO)
     assert torch.equal(y_tma, y_tc)
+    # IEEE half output: same arithmetic, rounding to 11 significant bits instead of 8.
+    y_half = L.linear_scaled(xd, wd, *full, dtype=torch.float16)
+    torch.cuda.synchronize()
+    ref = acc * rs[:, None] * cs[None, :] + b[None, :]
+    got = y_half.float().cpu().numpy()
+    assert y_half.dtype == torch.float16
+    assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0 ** -10 + 1e-3), float(np.max(np.abs(got - ref)))
 
 
 def test_bounded_wait_reports_and_recovers(cuda):
