@@ -128,6 +128,7 @@ __device__ __forceinline__ void drain_accumulator_scaled(uint32_t t_addr, int wi
 // row pitch of Y).  Column scales and biases: lane l fetches those of columns l and l + 32 of the
 // NEXT chunk while the current one is converted (two coalesced loads per vector instead of a
 // dependent chain of per-column loads), and the values reach the other lanes by shuffle.
+template <bool kHalf>
 __device__ __forceinline__ void drain_accumulator_scaled_tma(uint32_t t_addr, int width, int row0, int col0, int m, int n,
                                                              const ScaledOut& so, const CUtensorMap* tm_y16,
                                                              uint32_t stage0, uint32_t& chunk_no, int lane)
@@ -162,7 +163,13 @@ __device__ __forceinline__ void drain_accumulator_scaled_tma(uint32_t t_addr, in
             const float o0 = __shfl_sync(0xffffffffu, b_cur[hf], l0), o1 = __shfl_sync(0xffffffffu, b_cur[hf], l0 + 1);
             const float f0 = fmaf(static_cast<float>(static_cast<int>(v[hf][l0]) >> 8) * rs, s0, o0);
             const float f1 = fmaf(static_cast<float>(static_cast<int>(v[hf][l0 + 1]) >> 8) * rs, s1, o1);
-            h[j] = static_cast<uint32_t>(scaled_to_bits(f0, so.fp16)) | (static_cast<uint32_t>(scaled_to_bits(f1, so.fp16)) << 16);
+            if constexpr (kHalf) {  // the format is a compile-time choice here: this loop is the hot one
+                const __half2 pr = __floats2half2_rn(f0, f1);
+                h[j] = *reinterpret_cast<const uint32_t*>(&pr);
+            } else {
+                const __nv_bfloat162 pr = __floats2bfloat162_rn(f0, f1);
+                h[j] = *reinterpret_cast<const uint32_t*>(&pr);
+            }
         }
         const uint32_t stg = stage0 + (chunk_no & 1u) * 4096;
         if (lane == 0) tma_store_wait_read<1>();

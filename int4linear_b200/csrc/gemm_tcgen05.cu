@@ -293,7 +293,10 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
             if (so.y16 != nullptr) {
                 // Dequantised bf16 output; y_maps[0] then describes the bf16 matrix.
-                if constexpr (kTmaStore) drain_accumulator_scaled_tma(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
+                if constexpr (kTmaStore) {
+                    if (so.fp16) drain_accumulator_scaled_tma<true>(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
+                    else drain_accumulator_scaled_tma<false>(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
+                }
                 else drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
             } else
                 drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
