@@ -163,6 +163,16 @@ int int4_linear_host(const void* x_packed_h, const void* w_packed_h, void* y_h,
                      int m, int n, int k, int w_resident);
 
 /*
+ * Host packer with the reference's semantics (`pack` / `unpack`, utils/packer.h:5-6,
+ * utils/packer.cpp:3-31): src / dst are HOST arrays, m x n ints with one signed 4-bit value each
+ * on the unpacked side and m x ceil(n / 8) ints on the packed side (low nibble = even index, rows
+ * padded with zero nibbles).  The library also exports the C++ symbols `pack` and `unpack`
+ * themselves (declared in compat/utils/packer.h).
+ */
+void int4_linear_pack_host(const int* src_h, int* dst_h, int m, int n);
+void int4_linear_unpack_host(const int* src_h, int* dst_h, int m, int n);
+
+/*
  * Device-side forms of `void pack(const int* src, int* dst, int m, int n)` and
  * `void unpack(...)` (utils/packer.h:5-6, utils/packer.cpp:3-31): same bit layout, same
  * row padding to a multiple of eight elements, but source and destination are DEVICE

@@ -20,6 +20,8 @@ SYMBOLS = {
     "int4_linear_launch_prepared_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_launch_static_scratch_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),
+    "int4_linear_pack_host": (None, [_VP, _VP, _I, _I]),
+    "int4_linear_unpack_host": (None, [_VP, _VP, _I, _I]),
     "int4_linear_pack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_pack_i8": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_unpack_i32": (_I, [_VP, _VP, _I, _I, _VP]),

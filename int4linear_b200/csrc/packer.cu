@@ -170,3 +170,40 @@ int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols
 }
 
 }  // namespace i4l
+
+// ------------------------------------------------------------------ host side
+// Host packer with the reference's interface (utils/packer.h:5-6, utils/packer.cpp:3-31), so that a
+// program written against the reference links against this library alone: src holds one element
+// per int, a packed word holds eight nibbles, element 8w + j of a row in bits 4j .. 4j+3 of word w
+// (low nibble = even index); a row is padded with zero nibbles to a whole word.  unpack
+// sign-extends.  Plain loops over rows: these run outside any timed region, like the reference's.
+void pack(const int* src, int* dst, const int m, const int n)
+{
+    const int wpr = (n + 7) / 8;
+    for (int r = 0; r < m; ++r) {
+        const int* s = src + static_cast<size_t>(r) * n;
+        int* d = dst + static_cast<size_t>(r) * wpr;
+        for (int w = 0; w < wpr; ++w) {
+            uint32_t word = 0;
+            const int left = n - 8 * w < 8 ? n - 8 * w : 8;
+            for (int j = 0; j < left; ++j) word |= (static_cast<uint32_t>(s[8 * w + j]) & 0xFu) << (4 * j);
+            d[w] = static_cast<int>(word);
+        }
+    }
+}
+
+void unpack(const int* src, int* dst, const int m, const int n)
+{
+    const int wpr = (n + 7) / 8;
+    for (int r = 0; r < m; ++r) {
+        const int* s = src + static_cast<size_t>(r) * wpr;
+        int* d = dst + static_cast<size_t>(r) * n;
+        for (int c = 0; c < n; ++c) {
+            const uint32_t nib = (static_cast<uint32_t>(s[c >> 3]) >> (4 * (c & 7))) & 0xFu;
+            d[c] = static_cast<int>(nib ^ 8u) - 8;  // sign extension of a 4-bit two's-complement value
+        }
+    }
+}
+
+extern "C" void int4_linear_pack_host(const int* src, int* dst, int m, int n) { pack(src, dst, m, n); }
+extern "C" void int4_linear_unpack_host(const int* src, int* dst, int m, int n) { unpack(src, dst, m, n); }

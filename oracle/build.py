@@ -75,6 +75,8 @@ def build_dropin(force: bool = False) -> list[str]:
                                               linear_v21_launch resolved from the library
         oracle/_ref/benchmark_dropin          test/benchmark.cu + utils/packer.cpp, kernel
                                               template taken from the compat header
+        oracle/_ref/test_correctness_dropin_libonly   test/test_correctness.cu alone: the
+                                              packer comes from the library as well
     Only possible where the reference checkout exists; returns the files built."""
     if not reference_available():
         return []
@@ -99,6 +101,14 @@ def build_dropin(force: bool = False) -> list[str]:
         if force or not _newer(out, deps):
             subprocess.run(common + srcs + link + ["-o", out], check=True)
         built.append(out)
+    # The same correctness program linked against the library alone: pack / unpack come from the
+    # library too (compat/utils/packer.h), no source file of the reference besides the program.
+    out = os.path.join(out_dir, "test_correctness_dropin_libonly")
+    srcs = [os.path.join(REFERENCE_ROOT, "test/test_correctness.cu")]
+    deps = srcs + [lib, os.path.join(pkg, "compat", "kernels", "linear_v21.h"), os.path.join(pkg, "compat", "utils", "packer.h")]
+    if force or not _newer(out, deps):
+        subprocess.run(common + srcs + link + ["-o", out], check=True)
+    built.append(out)
     return built
 
 

@@ -29,6 +29,16 @@ def test_reference_correctness_program_runs_unchanged(cuda):
     assert "CUDA FAILED" not in r.stdout + r.stderr
 
 
+def test_reference_correctness_program_links_against_the_library_alone(cuda):
+    """The same program built without the reference's utils/packer.cpp: pack comes from the library."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "test_correctness_dropin_libonly")
+    if not os.path.exists(exe):
+        pytest.skip("built only where the reference checkout is available")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "CUDA FAILED" not in r.stdout + r.stderr
+
+
 def test_reference_gpu_kernel_agrees(cuda):
     """The reference's own GPU kernel (unmodified sources, sm_100a build in oracle/_ref), this
     library and the CPU oracle must give the same int32 matrix."""

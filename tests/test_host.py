@@ -23,6 +23,28 @@ def test_packer_matches_golden(path):
         assert np.array_equal(L.unpack_bytes(as_bytes), g["x"])
 
 
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: p.split("/")[-1][:-4])
+def test_native_host_packer_matches_golden(path):
+    """The library's own `pack` / `unpack` (C++ symbols with the reference's signatures, and their
+    C-ABI aliases) against fixtures produced by the reference's packer."""
+    import ctypes
+    lib = _lib.load()
+    g = np.load(path)
+    x = np.ascontiguousarray(g["x"].astype(np.int32))
+    m, n = x.shape
+    want = np.ascontiguousarray(g["x_packed"]).view(np.int32).reshape(m, -1)
+    for pack_name, unpack_name in (("int4_linear_pack_host", "int4_linear_unpack_host"), ("_Z4packPKiPiii", "_Z6unpackPKiPiii")):
+        pack_fn, unpack_fn = getattr(lib, pack_name), getattr(lib, unpack_name)
+        for fn in (pack_fn, unpack_fn):
+            fn.restype, fn.argtypes = None, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+        packed = np.full_like(want, -1)
+        pack_fn(x.ctypes.data, packed.ctypes.data, m, n)
+        assert np.array_equal(packed, want)
+        back = np.empty_like(x)
+        unpack_fn(packed.ctypes.data, back.ctypes.data, m, n)
+        assert np.array_equal(back, x)
+
+
 def test_pack_roundtrip_all_values():
     v = np.arange(-8, 8, dtype=np.int32).reshape(1, 16)
     p = L.pack(v)
