@@ -370,3 +370,40 @@ def test_random_shapes_through_the_dispatcher(cuda):
         ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
         assert O.is_same(y, ref), (m, n, k)
     assert L.last_status() == 0
+
+
+def test_concurrent_host_threads_on_their_own_streams(cuda):
+    """Four host threads launch different shapes on their own streams at the same time (shared
+    per-device context, tensor-map cache and launch counter behind the library's locks); every
+    result must be exact."""
+    import threading
+    import torch
+    shapes = [(300, 520, 256), (16, 1024, 4096), (1024, 1024, 512), (257, 130, 1056)]
+    cases = []
+    for i, (m, n, k) in enumerate(shapes):
+        x, w, xp, wp = make_case(m, n, k, seed=300 + i)
+        ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+        cases.append((torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda), k, ref))
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(idx):
+        try:
+            xd, wd, k, ref = cases[idx]
+            stream = torch.cuda.Stream(device=cuda)
+            with torch.cuda.stream(stream):
+                for _ in range(25):
+                    y = L.linear(xd, wd, k=k)
+                stream.synchronize()
+            if not O.is_same(y.cpu().numpy(), ref):
+                errors.append(f"thread {idx}: wrong result")
+        except Exception as e:  # noqa: BLE001
+            errors.append(f"thread {idx}: {e!r}")
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(cases))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert L.last_status() == 0
