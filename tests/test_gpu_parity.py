@@ -93,7 +93,7 @@ def test_skinny_kernel(cuda, shape):
 
 def test_extreme_values_closed_form(cuda):
     """All -8 times all -8 is the largest accumulator the format can produce: 64*K per element."""
-    for k in (128, 8192, 65536):
+    for k in (128, 8192, 65536, 131040):  # 131040 is the largest K the 256-fold scaled accumulator allows
         m, n = 130, 72
         xp = np.full((m, k // 2), 0x88, dtype=np.uint8)
         wp = np.full((n, k // 2), 0x88, dtype=np.uint8)
