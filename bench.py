@@ -211,9 +211,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--path", default="auto", choices=["auto", "tcgen05", "legacy", "skinny"],
                     help="force one kernel family of this library (default: shape dispatch)")
-    ap.add_argument("--variant", default="default", choices=["default", "two-pass", "prepared", "x-tmem"],
+    ap.add_argument("--variant", default="default", choices=["default", "two-pass", "prepared"],
                     help="opt-in variants of the tensor-memory path: expand pre-pass + byte GEMM, weights "
-                         "pre-expanded outside the timed region, X operand in tensor memory")
+                         "pre-expanded outside the timed region")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -286,8 +286,6 @@ def main():
 
     if args.variant == "two-pass":
         L.set_two_pass(1)
-    elif args.variant == "x-tmem":
-        L.set_tuning(0, False, 2)
     w_prepared = L.prepare_weights(wd) if args.variant == "prepared" else None
 
     def step(i):

@@ -208,9 +208,8 @@ int int4_linear_set_path(int path);
  * single-CTA output tile; direct_store != 0 makes the epilogue write Y with
  * per-thread vector stores instead of shared-memory staging + TMA stores
  * (always used when n % 4 != 0); cta_pairs = 1 forces the 256 x 256 tile on a
- * two-CTA cluster (cta_group::2) with both operands in shared memory, 2 the
- * 256 x 192 pair tile whose X operand lives in tensor memory, 0 forbids
- * pairs, -1 leaves the choice to the dispatcher.
+ * two-CTA cluster (cta_group::2), 0 forbids pairs, -1 leaves the choice to the
+ * dispatcher.
  * Environment: INT4L_TILE_N, INT4L_EPILOGUE=direct, INT4L_PAIRS. */
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
 

@@ -18,7 +18,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libint4linear_b200.so")
-SOURCES = ["api.cu", "gemm_tcgen05.cu", "gemm_tcgen05_ts.cu", "gemm_tcgen05_s8.cu", "gemm_skinny.cu", "gemm_legacy.cu", "packer.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "gemm_tcgen05.cu", "gemm_tcgen05_s8.cu", "gemm_skinny.cu", "gemm_legacy.cu", "packer.cu", "no_alloc.cu"]
 
 
 def _deps() -> list[str]:
@@ -36,8 +36,8 @@ def needs_build() -> bool:
 
 def build(force: bool = False, verbose: bool = False, out: str | None = None,
           extra_flags: list[str] | None = None) -> str:
-    """Build the library.  `out` / `extra_flags` produce a variant (for example a
-    -DI4L_TRACE timeline build) next to the regular one without replacing it."""
+    """Build the library.  `out` / `extra_flags` produce a variant next to the regular one
+    without replacing it."""
     if out is None and not force and not needs_build():
         return LIB
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"

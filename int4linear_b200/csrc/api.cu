@@ -17,7 +17,7 @@ namespace {
 constexpr int kMaxDevices = 64;
 DeviceCtx g_ctx[kMaxDevices];
 bool g_ctx_ready[kMaxDevices];
-std::mutex g_mutex;          // contexts and the host-buffer staging
+std::mutex g_mutex;          // creation of the per-device contexts
 std::mutex g_tm_mutex;       // tensor-map cache
 std::mutex g_scratch_mutex;  // two-pass scratch (taken inside dispatch, which may run under g_mutex)
 std::atomic<long long> g_launches{0};
@@ -85,8 +85,8 @@ int forced_tile_n()
 {
     int v = g_tile_n.load();
     if (v == 0) {
-        const char* e = std::getenv("INT4L_TILE_N");
-        if (e) v = std::atoi(e);
+        static const int from_env = [] { const char* e = std::getenv("INT4L_TILE_N"); return e ? std::atoi(e) : 0; }();
+        v = from_env;
     }
     return v;
 }
@@ -121,7 +121,7 @@ int forced_pairs()
     if (v == -2) {
         const char* e = std::getenv("INT4L_PAIRS");
         v = e ? std::atoi(e) : -1;
-        if (v < -1 || v > 2) v = -1;
+        if (v < -1 || v > 1) v = -1;
         g_pairs.store(v);
     }
     return v;
@@ -165,7 +165,6 @@ DeviceCtx* current_ctx(int* status)
     c->encode_tiled = fn;
 
     int rc = setup_tcgen05(c);
-    if (rc == INT4L_OK) rc = setup_tcgen05_ts(c);
     if (rc == INT4L_OK) rc = setup_tcgen05_s8(c);
     if (rc == INT4L_OK) rc = setup_skinny(c);
     if (rc != INT4L_OK) { *status = rc; return nullptr; }
@@ -505,7 +504,9 @@ int int4_linear_host(const void* x_h, const void* w_h, void* y_h, int m, int n, 
     const size_t xb = static_cast<size_t>(m) * k / 2, wb = static_cast<size_t>(n) * k / 2;
     const size_t yb = static_cast<size_t>(m) * n * 4;
     {
-        std::lock_guard<std::mutex> lock(g_mutex);
+        // One host-buffer call at a time per DEVICE (the staging buffers and the three pipeline
+        // streams belong to the device's context); calls on different devices run concurrently.
+        std::lock_guard<std::mutex> lock(ctx->host_mutex);
         const bool w_buf_grew = ctx->stage_w_bytes < wb;
         rc = ensure_stage(&ctx->stage_x, &ctx->stage_x_bytes, xb);
         if (rc == INT4L_OK) rc = ensure_stage(&ctx->stage_w, &ctx->stage_w_bytes, wb);
@@ -514,14 +515,15 @@ int int4_linear_host(const void* x_h, const void* w_h, void* y_h, int m, int n, 
         const bool reuse = w_resident && !w_buf_grew && ctx->stage_w_src == w_h && ctx->stage_w_src_bytes == wb;
         if (m >= 1024 && yb >= (16u << 20)) {
             rc = host_pipelined(ctx, x_h, w_h, y_h, m, n, k, reuse);
+            // The weights count as resident only when their upload went through.
+            if (rc != INT4L_OK) { ctx->stage_w_src = nullptr; ctx->stage_w_src_bytes = 0; t_last_status = rc; return rc; }
             if (!reuse) { ctx->stage_w_src = w_h; ctx->stage_w_src_bytes = wb; }
-            if (rc != INT4L_OK) { t_last_status = rc; return rc; }
         } else {
             cudaError_t e = cudaMemcpyAsync(ctx->stage_x, x_h, xb, cudaMemcpyHostToDevice, nullptr);
             if (e == cudaSuccess && !reuse) {
                 e = cudaMemcpyAsync(ctx->stage_w, w_h, wb, cudaMemcpyHostToDevice, nullptr);
-                ctx->stage_w_src = w_h;
-                ctx->stage_w_src_bytes = wb;
+                ctx->stage_w_src = e == cudaSuccess ? w_h : nullptr;
+                ctx->stage_w_src_bytes = e == cudaSuccess ? wb : 0;
             }
             if (e != cudaSuccess) { cudaGetLastError(); t_last_status = INT4L_ERR_CUDA; return INT4L_ERR_CUDA; }
             Problem p{ctx->stage_x, ctx->stage_w, ctx->stage_y, m, n, k};
@@ -623,7 +625,7 @@ int int4_linear_set_two_pass(int mode)
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
 {
     if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256) return INT4L_ERR_INVALID_ARG;
-    if (cta_pairs < -1 || cta_pairs > 2) return INT4L_ERR_INVALID_ARG;
+    if (cta_pairs < -1 || cta_pairs > 1) return INT4L_ERR_INVALID_ARG;
     g_tile_n.store(tile_n);
     g_direct_store.store(direct_store ? 1 : 0);
     g_pairs.store(cta_pairs);
@@ -670,20 +672,3 @@ void linear_v21_launch(void* x_packed_d, void* w_packed_d, void* y_d, int m, int
 {
     int4_linear_launch(x_packed_d, w_packed_d, y_d, m, n, k);
 }
-
-// The launchers of the reference's earlier kernel generations (kernels/linear_v0.h:168,
-// linear_v1.h:208, linear_v2.h:284, and the same declaration at the end of linear_v10.h,
-// linear_v11.h and linear_v20.h) have the same signature and contract; call sites written against
-// any of them get the same sm_100a kernels.
-#define I4L_LEGACY_LAUNCHER(name)                                                              \
-    void name(void* x_packed_d, void* w_packed_d, void* y_d, int m, int n, int k)                \
-    {                                                                                          \
-        int4_linear_launch(x_packed_d, w_packed_d, y_d, m, n, k);                              \
-    }
-I4L_LEGACY_LAUNCHER(linear_v0_launch)
-I4L_LEGACY_LAUNCHER(linear_v1_launch)
-I4L_LEGACY_LAUNCHER(linear_v2_launch)
-I4L_LEGACY_LAUNCHER(linear_v10_launch)
-I4L_LEGACY_LAUNCHER(linear_v11_launch)
-I4L_LEGACY_LAUNCHER(linear_v20_launch)
-#undef I4L_LEGACY_LAUNCHER

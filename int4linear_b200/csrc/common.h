@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/int4linear_b200.h"
 
 namespace i4l {
@@ -72,7 +74,9 @@ struct DeviceCtx {
     int* status_dev = nullptr;
     // cuTensorMapEncodeTiled, resolved through the runtime (no libcuda link).
     void* encode_tiled = nullptr;
-    // Device scratch owned by the host-buffer entry point.
+    // Device scratch owned by the host-buffer entry point; host_mutex serialises its users on
+    // this device only.
+    std::mutex host_mutex;
     void* stage_x = nullptr; size_t stage_x_bytes = 0;
     void* stage_w = nullptr; size_t stage_w_bytes = 0;
     void* stage_y = nullptr; size_t stage_y_bytes = 0;
@@ -111,7 +115,6 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 // GEMM on operands already expanded to bytes (second pass of the two-pass path).
 int launch_tcgen05_s8(DeviceCtx* ctx, const Problem& p, const void* x_bytes, const void* w_bytes, cudaStream_t stream);
 int launch_tcgen05_gather(DeviceCtx* ctx, const Problem& p, const GatherDst& g, cudaStream_t stream);
-int launch_tcgen05_ts(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);  // X operand in tensor memory
 int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 int launch_legacy(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
 
@@ -125,7 +128,6 @@ int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols
 
 // One-off function attribute set-up (dynamic shared memory opt-in).
 int setup_tcgen05(DeviceCtx* ctx);
-int setup_tcgen05_ts(DeviceCtx* ctx);
 int setup_tcgen05_s8(DeviceCtx* ctx);
 int setup_skinny(DeviceCtx* ctx);
 
@@ -141,6 +143,6 @@ bool getenv_flag_direct_store();
 int forced_tile_n();
 int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
 int two_pass_mode();  // -1 automatic, 0 never, 1 whenever the tensor-memory family is used
-int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 pairs with both operands in smem, 2 pairs with X in TMEM
+int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always (m > 128)
 
 }  // namespace i4l

@@ -421,6 +421,27 @@ gemm_s4_skinny_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const uint8_
     }
 }
 
+// Experiment knobs of the decode kernels, read from the environment once per process (a decode
+// launch lasts microseconds; a getenv per launch would show):
+//   INT4L_SKINNY_CTAS_PER_SM = 1 | 2   CTAs per SM of the register variant
+//   INT4L_SKINNY_ROWS / INT4L_SKINNY_BUFS   stage geometry of the TMA variant
+struct SkinnyEnv {
+    int ctas_per_sm = 0, stage_rows = 0, n_buffers = 2;
+};
+const SkinnyEnv& skinny_env()
+{
+    static const SkinnyEnv env = [] {
+        SkinnyEnv v;
+        if (const char* e = getenv("INT4L_SKINNY_CTAS_PER_SM")) v.ctas_per_sm = atoi(e) == 1 ? 1 : 2;
+        if (const char* e = getenv("INT4L_SKINNY_ROWS")) {
+            v.stage_rows = atoi(e);
+            if (const char* b = getenv("INT4L_SKINNY_BUFS")) v.n_buffers = atoi(b);
+        }
+        return v;
+    }();
+    return env;
+}
+
 struct SkinnyPlan {
     int mb, grid, groups_total, groups_per_cta_max, x_pitch;
     size_t smem;
@@ -493,7 +514,7 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         // One CTA per SM when launches may fully overlap (two launches then share each SM);
         // otherwise two, which hides more latency inside a single launch.
         int ctas_per_sm = overlap == 2 ? 1 : 2;
-        if (const char* e = getenv("INT4L_SKINNY_CTAS_PER_SM")) ctas_per_sm = atoi(e) == 1 ? 1 : 2;
+        if (skinny_env().ctas_per_sm) ctas_per_sm = skinny_env().ctas_per_sm;
         const int grid = s.groups_total < ctas_per_sm * ctx->sm_count ? s.groups_total : ctas_per_sm * ctx->sm_count;
         const int per_cta = (s.groups_total + grid - 1) / grid;
         cudaLaunchConfig_t cfg = {};
@@ -528,10 +549,9 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
             stage_rows = 48;
             n_buffers = 2;
         }
-        if (const char* e = getenv("INT4L_SKINNY_ROWS")) {  // experiment: explicit stage geometry
-            stage_rows = atoi(e);
-            const char* b = getenv("INT4L_SKINNY_BUFS");
-            n_buffers = b ? atoi(b) : 2;
+        if (skinny_env().stage_rows) {  // experiment: explicit stage geometry
+            stage_rows = skinny_env().stage_rows;
+            n_buffers = skinny_env().n_buffers;
         }
         const size_t smem = fixed + 16ull * n_buffers * stage_rows * 128;
         if (smem <= 227 * 1024 && skinny_variant() != 1) {

@@ -48,8 +48,6 @@
 #include "ptx.cuh"
 #include "epilogue.cuh"
 
-#define I4L_TRACE_EXPORT int4_linear_debug_trace
-#include "trace.cuh"
 
 namespace i4l {
 
@@ -130,7 +128,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
     const uint32_t cta_rank = CTAS == 2 ? cluster_cta_rank() : 0u;
     const int worker = CTAS == 2 ? static_cast<int>(cluster_id_x()) : static_cast<int>(blockIdx.x);
     const int workers = CTAS == 2 ? static_cast<int>(cluster_count_x()) : static_cast<int>(gridDim.x);
-    I4L_TRACE_CLK(0);
 
     // Barrier set-up by the lanes of warp 2 in parallel (one barrier each; a single thread takes
     // over a thousand cycles for the two dozen of them), tensor-map prefetch by thread 0.
@@ -158,11 +155,9 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
     // cluster barrier -- "the other CTA's barriers exist" -- is split into an arrive here and a
     // wait in each role just before its first access to the peer.
     __syncthreads();
-    if (tid == 0) I4L_TRACE_PUT(0, 1, 3);
     if constexpr (CTAS == 2) {
         if (warp == 0) cluster_arrive_relaxed(); else cluster_arrive_release();
     }
-    if (tid == 0) I4L_TRACE_PUT(0, 2, 2);
     uint32_t tmem_base = 0;
     if (warp >= 1 && warp < 6) {
         if (warp == 1) {
@@ -216,9 +211,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 const int rows_w = width / CTAS;
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const uint32_t s = it % P, r = it / P;
-                    I4L_TRACE_PUT(0, it, 0);
                     if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
-                    I4L_TRACE_PUT(0, it, 1);
                     mbar_expect_tx(pk_full(s), C::kPreW ? C::kPkStage : (kBM + rows_w) * kBKBytes);
                     const uint32_t dst = pk_base + s * C::kPkStage;
                     tma_load_2d(dst, &tm_x, pk_full(s), kb * kBKBytes, (tm * CTAS + cta_rank) * kBM);
@@ -252,9 +245,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const uint32_t s = it % U, r = it / U;
-                    I4L_TRACE_PUT(1, it, 0);
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
-                    I4L_TRACE_PUT(1, it, 1);
                     tc_fence_after_sync();
                     const uint32_t a_addr = up_base + s * C::kUpStage;
                     const uint64_t a_desc = umma_desc_sw128(a_addr);
@@ -265,7 +256,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                         umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
                     if constexpr (CTAS == 2) umma_commit_2cta(up_empty(s), 3); else umma_commit(up_empty(s));
-                    I4L_TRACE_PUT(1, it, 2);
                 }
                 if (alive) {
                     if constexpr (CTAS == 2) umma_commit_2cta(tm_full(buf), 3); else umma_commit(tm_full(buf));
@@ -284,9 +274,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             int tm, tn, col_off, width;
             item_coord(item, tm, tn, col_off, width);
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
-            if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 0);
             if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
-            if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 1);
             tc_fence_after_sync();
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
@@ -305,7 +293,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             if (lane == 0) {
                 if constexpr (CTAS == 2) mbar_arrive_cluster(tm_empty(buf), 0); else mbar_arrive(tm_empty(buf));
             }
-            if (warp == 2 && lane == 0) I4L_TRACE_PUT(3, local_tile, 2);
         }
         if (kTmaStore && lane == 0) tma_store_wait_all<0>();
         __syncwarp();
@@ -334,9 +321,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
-                if (gtid == 0) I4L_TRACE_PUT(2, it, 0);
                 if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
-                if (gtid == 0) I4L_TRACE_PUT(2, it, 1);
                 const uint32_t src = pk_base + ps * C::kPkStage;
                 const uint32_t dst = up_base + us * C::kUpStage;
                 // All loads first, so their latencies overlap.
@@ -345,7 +330,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 for (int i = 0; i < kPerThread; ++i)
                     if (i * kGroupThreads + gtid < chunks) x[i] = lds128(src + (i * kGroupThreads + gtid) * 16);
                 if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
-                if (gtid == 0) I4L_TRACE_PUT(2, it, 2);
 #pragma unroll
                 for (int i = 0; i < kPerThread; ++i) {
                     const int q = i * kGroupThreads + gtid;
@@ -361,21 +345,16 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                     sts128(rowaddr + (((2 * c) ^ sw) << 4), lo);
                     sts128(rowaddr + (((2 * c + 1) ^ sw) << 4), hi);
                 }
-                if (gtid == 0) I4L_TRACE_PUT(4, it, 0);
                 fence_proxy_async_smem();
-                if (gtid == 0) I4L_TRACE_PUT(4, it, 1);
                 if constexpr (C::kPreW) {
                     // The slot is complete only when TMA has also delivered its expanded W rows.
                     if (!mbar_wait(w_full(us), ur & 1u, abort_flag)) { alive = false; break; }
                 }
                 __syncwarp();
-                if (gtid == 0) I4L_TRACE_PUT(4, it, 2);
                 if (lane == 0) {
                     if constexpr (CTAS == 2) mbar_arrive_cluster(up_full(us), 0); else mbar_arrive(up_full(us));
-                    if (gtid == 0) I4L_TRACE_PUT(4, it, 3);
                     mbar_arrive(pk_empty(ps));
                 }
-                if (gtid == 0) I4L_TRACE_PUT(2, it, 3);
             }
         }
     }
@@ -383,7 +362,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
     // ------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    I4L_TRACE_CLK(1);
     if (*abort_flag) {
         // Something never arrived.  Report, give copies in flight time to land,
         // then release tensor memory so the SM stays usable.
@@ -614,7 +592,6 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     const int forced = forced_tile_n();
     if (forced == 64 || forced == 128 || forced == 256) { bn = forced; pairs = false; }
     if (forced_pairs() >= 0) pairs = forced_pairs() != 0;
-    if (pairs && forced_pairs() == 2 && p.scaled.y16 == nullptr) return launch_tcgen05_ts(ctx, p, stream);
     if (pairs) return tma_store ? launch_cfg<Cfg256x2, true>(ctx, p, stream) : launch_cfg<Cfg256x2, false>(ctx, p, stream);
     if (bn == 256) return tma_store ? launch_cfg<Cfg256, true>(ctx, p, stream) : launch_cfg<Cfg256, false>(ctx, p, stream);
     if (bn == 128) return tma_store ? launch_cfg<Cfg128, true>(ctx, p, stream) : launch_cfg<Cfg128, false>(ctx, p, stream);

@@ -107,6 +107,10 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias
         raise ValueError("packed widths do not match k")
     if out is None:
         out = torch.empty((m, n), dtype=torch.int32, device=x_packed.device)
+    elif tuple(out.shape) != (m, n) or out.dtype != torch.int32 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int32 tensor of shape [m, n]")
+    if m == 0 or n == 0:
+        return out  # nothing to compute (a rank whose shard of W is empty)
     if stream is None:
         handle = torch.cuda.current_stream(x_packed.device).cuda_stream
     else:
@@ -150,7 +154,9 @@ def linear_scaled(x_packed, w_packed, row_scale=None, col_scale=None, bias=None,
         out = torch.empty((m, n), dtype=dtype or torch.bfloat16, device=xb.device)
     if out.dtype not in (torch.bfloat16, torch.float16) or (dtype is not None and out.dtype != dtype):
         raise ValueError("the scaled output is bfloat16 or float16")
-    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    if tuple(out.shape) != (m, n) or not out.is_contiguous() or out.device != xb.device:
+        raise ValueError("out must be a contiguous [m, n] tensor on the operands' device")
+    handle = (stream or torch.cuda.current_stream(xb.device)).cuda_stream
     ptr = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
     lib = _lib.load()
     fn = lib.int4_linear_scaled_f16_launch_async if out.dtype == torch.float16 else lib.int4_linear_scaled_launch_async
@@ -169,7 +175,7 @@ def prepare_weights(w_packed, k: int | None = None, stream=None):
     n = wb.shape[0]
     k = k or wb.shape[1] * 2
     out = torch.empty((n, k), dtype=torch.uint8, device=wb.device)
-    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    handle = (stream or torch.cuda.current_stream(wb.device)).cuda_stream
     with torch.cuda.device(wb.device):
         st = _lib.load().int4_linear_prepare_weights(wb.data_ptr(), out.data_ptr(), n, k, handle)
     if st != 0:
@@ -187,7 +193,9 @@ def linear_prepared(x_packed, w_expanded, out=None, bias=None, stream=None):
         raise ValueError("w_expanded must be the contiguous [n, k] uint8 tensor made by prepare_weights")
     if out is None:
         out = torch.empty((m, n), dtype=torch.int32, device=xb.device)
-    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    elif tuple(out.shape) != (m, n) or out.dtype != torch.int32 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int32 tensor of shape [m, n]")
+    handle = (stream or torch.cuda.current_stream(xb.device)).cuda_stream
     with torch.cuda.device(xb.device):
         st = _lib.load().int4_linear_launch_prepared_async(
             xb.data_ptr(), w_expanded.data_ptr(), bias.data_ptr() if bias is not None else None,

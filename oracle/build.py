@@ -21,7 +21,10 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_ROOT = os.environ.get("INT4LINEAR_REFERENCE_ROOT", "/root/reference")
+# The reference checkout: named by INT4LINEAR_REFERENCE_ROOT, else a directory called
+# `reference` beside this repository.  Where neither exists only the prebuilt files are used.
+REFERENCE_ROOT = os.environ.get("INT4LINEAR_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target: str, sources: list[str]) -> bool:

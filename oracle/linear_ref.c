@@ -14,7 +14,7 @@
  * Parity pin: the reference ships no golden vectors (its own comparison is
  * commented out, test/test_correctness.cu:66-76), so this file is pinned by
  * running it against the reference's own pack / unpack / linear_ref compiled
- * from the reference tree (see build_ref.py) and by the fixtures under
+ * from the reference tree (see build.py in this directory) and by the fixtures under
  * tests/golden/ that were produced by that compiled reference code.
  *
  * All arithmetic is integer; OpenMP parallelism over output rows cannot change

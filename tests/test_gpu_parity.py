@@ -35,8 +35,6 @@ VARIANTS = [
     ("tcgen05-64-direct", dict(path=L.PATH_TCGEN05, tile_n=64, direct=True)),
     ("tcgen05-pairs-tma", dict(path=L.PATH_TCGEN05, pairs=1)),
     ("tcgen05-pairs-direct", dict(path=L.PATH_TCGEN05, pairs=1, direct=True)),
-    ("tcgen05-pairs-xtmem-tma", dict(path=L.PATH_TCGEN05, pairs=2)),
-    ("tcgen05-pairs-xtmem-direct", dict(path=L.PATH_TCGEN05, pairs=2, direct=True)),
     ("two-pass-tma", dict(path=L.PATH_TCGEN05, two_pass=1)),
     ("two-pass-direct", dict(path=L.PATH_TCGEN05, two_pass=1, direct=True)),
     ("legacy", dict(path=L.PATH_LEGACY)),
@@ -220,7 +218,7 @@ def test_overlapped_launches_stay_exact(cuda, mode):
 
 @pytest.mark.parametrize("shape,variant", [
     ((300, 520, 256), dict(path=L.PATH_TCGEN05, pairs=1)),
-    ((300, 520, 256), dict(path=L.PATH_TCGEN05, pairs=2, direct=True)),
+    ((300, 520, 256), dict(path=L.PATH_TCGEN05, pairs=1, direct=True)),
     ((200, 77, 160), dict(path=L.PATH_TCGEN05, pairs=0)),
     ((16, 1000, 4096), dict(path=L.PATH_SKINNY)),
     ((40, 264, 1024), dict(path=L.PATH_SKINNY)),
