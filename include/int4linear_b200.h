@@ -132,6 +132,18 @@ int int4_linear_launch_prepared_async(const void* x_packed_d, const void* w_expa
                                       void* y_d, int m, int n, int k, void* stream);
 
 /*
+ * The operator on operands that were BOTH expanded beforehand with int4_linear_prepare_weights
+ * (which expands any packed matrix: pass X and its row count as well): x_expanded_d is m x k
+ * bytes, w_expanded_d n x k bytes.  A pure 8-bit GEMM -- TMA straight into the ring the tensor
+ * core reads, no unpack stage -- with the same results bit for bit.  It is the second pass of the
+ * two-pass path made callable by itself, for callers that keep activations expanded across
+ * several layers, and it is what bench.py times to measure the 8-bit tensor rate this library's
+ * own pipeline reaches on the device.  No reference counterpart.
+ */
+int int4_linear_launch_expanded_async(const void* x_expanded_d, const void* w_expanded_d, const int* bias_d,
+                                      void* y_d, int m, int n, int k, void* stream);
+
+/*
  * The two-pass operator (expand pre-pass + byte GEMM, see int4_linear_set_two_pass) for callers
  * that are not allowed to allocate device memory: servers or frameworks that have handed the
  * whole GPU to their own allocator, loops that cannot take the device-wide synchronisation of
@@ -144,8 +156,8 @@ int int4_linear_launch_prepared_async(const void* x_packed_d, const void* w_expa
  * device.  The array is shared by all calls and keeps the previous call's bytes (each call
  * overwrites what it reads, nothing has to be cleared); calls that could overlap on one GPU race
  * on it, so keep them ordered on one stream per device.  Same arguments and results as
- * int4_linear_bias_launch_async; a device-side timeout of this entry point is not reported
- * through int4_linear_last_status.
+ * int4_linear_bias_launch_async; a device-side timeout is reported by int4_linear_last_status
+ * (which reads this entry point's status word back with a symbol copy, again without allocating).
  */
 int int4_linear_launch_static_scratch_async(const void* x_packed_d, const void* w_packed_d, const int* bias_d,
                                             void* y_d, int m, int n, int k, void* stream);
@@ -188,6 +200,13 @@ int int4_linear_unpack_i32(const void* src_d, int* dst_d, int rows, int cols, vo
  * the kernels raise when a bounded wait expires (and clears it). */
 int int4_linear_last_status(void);
 
+/* Measurement aid for the HBM-bound decode shapes: one read-only streaming pass over `bytes`
+ * bytes at src_d (16-byte aligned), issued like the decode kernels' weight loads, XOR of the data
+ * into *sink_d.  Its time for the bytes of a weight matrix is the floor for one launch of a kernel
+ * that must read them once; bench.py reports it beside the decode kernel.  No reference
+ * counterpart. */
+int int4_linear_probe_stream_read(const void* src_d, unsigned long long bytes, unsigned* sink_d, void* stream);
+
 /* Self-test of the in-kernel failure handling, safe to run on a shared GPU: launches one warp
  * that waits for at most budget_ms (1..100) on a barrier nothing will ever signal, exactly as a
  * GEMM kernel would after a lost arrival.  The kernel must return by itself; afterwards
@@ -212,6 +231,16 @@ int int4_linear_set_path(int path);
  * dispatcher.
  * Environment: INT4L_TILE_N, INT4L_EPILOGUE=direct, INT4L_PAIRS. */
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
+
+/* How the tensor-memory kernels run a last wave of output tiles that does not fill the GPU:
+ * -1 (default) automatic; 0 as whole tiles; 1 as half-width items when at most half of the CTA
+ * pairs would be busy; 2 cut along K into equal shares for all workers, the partial sums of a
+ * tile being added into Y by bulk reductions after the share that holds the start of K has stored
+ * its part (integer addition: the result is bit-identical whatever the order).  Mode 2 applies to
+ * int32 output on one GPU only; the automatic choice uses it where it saves time, else mode 1.
+ * Replaces the fixed one-CTA-per-tile grid of kernels/linear_v21.cu:20-37.
+ * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_TAIL=none|half|streamk. */
+int int4_linear_set_tail(int mode);
 
 /* Overlap of back-to-back decode-shape launches in one stream (programmatic dependent
  * launch).  0 (default): every launch waits for the preceding work in its stream, as any

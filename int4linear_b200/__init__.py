@@ -15,6 +15,7 @@ from .linear import (  # noqa: F401
     linear,
     linear_host,
     linear_prepared,
+    linear_expanded,
     linear_scaled,
     prepare_weights,
     linear_v21_launch,
@@ -23,6 +24,7 @@ from .linear import (  # noqa: F401
     path_for,
     set_path,
     set_overlap,
+    set_tail,
     set_two_pass,
     set_tuning,
     PATH_AUTO,

@@ -18,6 +18,7 @@ SYMBOLS = {
     "int4_linear_launch_gather_async": (_I, [_VP, _VP, _VP, ctypes.POINTER(ctypes.c_void_p), _I, _I, _I, _I, _I, _I, _VP]),
     "int4_linear_prepare_weights": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_launch_prepared_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "int4_linear_launch_expanded_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_launch_static_scratch_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_host": (_I, [_VP, _VP, _VP, _I, _I, _I, _I]),
     "int4_linear_pack_host": (None, [_VP, _VP, _I, _I]),
@@ -25,12 +26,14 @@ SYMBOLS = {
     "int4_linear_pack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_pack_i8": (_I, [_VP, _VP, _I, _I, _VP]),
     "int4_linear_unpack_i32": (_I, [_VP, _VP, _I, _I, _VP]),
+    "int4_linear_probe_stream_read": (_I, [_VP, ctypes.c_ulonglong, _VP, _VP]),
     "int4_linear_selftest_timeout": (_I, [_I]),
     "int4_linear_last_status": (_I, []),
     "int4_linear_status_string": (ctypes.c_char_p, [_I]),
     "int4_linear_set_path": (_I, [_I]),
     "int4_linear_set_tuning": (_I, [_I, _I, _I]),
     "int4_linear_set_overlap": (_I, [_I]),
+    "int4_linear_set_tail": (_I, [_I]),
     "int4_linear_set_two_pass": (_I, [_I]),
     "int4_linear_path_for": (_I, [_I, _I, _I]),
     "int4_linear_device_info": (_I, [_I]),

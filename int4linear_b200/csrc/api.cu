@@ -27,6 +27,7 @@ std::atomic<int> g_direct_store{-1};
 std::atomic<int> g_overlap{-1};    // -1 = not yet read from the environment
 std::atomic<int> g_two_pass{-2};   // -2 = not yet read from the environment
 std::atomic<int> g_pairs{-2};      // -2 = not yet read from the environment
+std::atomic<int> g_tail{-2};       // -2 = not yet read from the environment
 thread_local int t_last_status = INT4L_OK;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -123,6 +124,20 @@ int forced_pairs()
         v = e ? std::atoi(e) : -1;
         if (v < -1 || v > 1) v = -1;
         g_pairs.store(v);
+    }
+    return v;
+}
+
+int tail_mode()
+{
+    int v = g_tail.load();
+    if (v == -2) {
+        const char* e = std::getenv("INT4L_TAIL");
+        v = -1;
+        if (e && !std::strcmp(e, "none")) v = 0;
+        else if (e && !std::strcmp(e, "half")) v = 1;
+        else if (e && !std::strcmp(e, "streamk")) v = 2;
+        g_tail.store(v);
     }
     return v;
 }
@@ -272,7 +287,11 @@ int poll_device_status(DeviceCtx* ctx)
 {
     if (!ctx || !ctx->status_host) return INT4L_OK;
     int s = *ctx->status_host;
-    if (s != INT4L_OK) *ctx->status_host = INT4L_OK;
+    if (s != INT4L_OK) {
+        *ctx->status_host = INT4L_OK;
+        // A kernel that gave up may have left hand-over flags raised; the next launch needs them clear.
+        if (ctx->sk_flags != nullptr && cudaMemset(ctx->sk_flags, 0, ctx->sk_flag_bytes) != cudaSuccess) cudaGetLastError();
+    }
     return s;
 }
 
@@ -434,6 +453,20 @@ int int4_linear_launch_prepared_async(const void* x, const void* w_expanded_d, c
     return rc;
 }
 
+int int4_linear_launch_expanded_async(const void* x_expanded_d, const void* w_expanded_d, const int* bias_d, void* y,
+                                      int m, int n, int k, void* stream)
+{
+    int rc = check_args(x_expanded_d, w_expanded_d, y, m, n, k);
+    if (rc == INT4L_OK && bias_d != nullptr && (reinterpret_cast<uintptr_t>(bias_d) & 3u)) rc = INT4L_ERR_MISALIGNED;
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{nullptr, nullptr, y, m, n, k, bias_d};
+    rc = launch_tcgen05_s8(ctx, p, x_expanded_d, w_expanded_d, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
 static int scaled_launch(const void* x, const void* w, const float* row_scale_d, const float* col_scale_d,
                          const float* bias_d, void* y16_d, int fp16, int m, int n, int k, void* stream)
 {
@@ -569,6 +602,15 @@ int int4_linear_unpack_i32(const void* src_d, int* dst_d, int rows, int cols, vo
     return rc;
 }
 
+int int4_linear_probe_stream_read(const void* src_d, unsigned long long bytes, unsigned* sink_d, void* stream)
+{
+    if (!src_d || !sink_d || bytes < 16 || (reinterpret_cast<uintptr_t>(src_d) & 15u)) return INT4L_ERR_INVALID_ARG;
+    int rc = INT4L_OK;
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) return rc;
+    return launch_stream_read(ctx, src_d, static_cast<size_t>(bytes), sink_d, static_cast<cudaStream_t>(stream));
+}
+
 int int4_linear_selftest_timeout(int budget_ms)
 {
     if (budget_ms < 1 || budget_ms > 100) return INT4L_ERR_INVALID_ARG;
@@ -589,6 +631,7 @@ int int4_linear_last_status(void)
         st = poll_device_status(&g_ctx[dev]);
     else
         cudaGetLastError();
+    if (st == INT4L_OK) st = poll_static_scratch_status();
     if (st != INT4L_OK) t_last_status = st;
     return t_last_status;
 }
@@ -629,6 +672,13 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
     g_tile_n.store(tile_n);
     g_direct_store.store(direct_store ? 1 : 0);
     g_pairs.store(cta_pairs);
+    return INT4L_OK;
+}
+
+int int4_linear_set_tail(int mode)
+{
+    if (mode < -1 || mode > 2) return INT4L_ERR_INVALID_ARG;
+    g_tail.store(mode);
     return INT4L_OK;
 }
 

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/int4linear_b200.h"
@@ -88,6 +89,10 @@ struct DeviceCtx {
     size_t stage_w_src_bytes = 0;
     // Scratch of the two-pass path (expanded operands), grown on demand.
     void* scratch = nullptr; size_t scratch_bytes = 0;
+    // Hand-over flags of the tiles the tensor-memory kernel cuts along K, and how many launches
+    // have taken a set of them.
+    unsigned* sk_flags = nullptr; size_t sk_flag_bytes = 0;
+    std::atomic<unsigned long long> sk_launches{0};
     bool attrs_set = false;
 };
 
@@ -126,10 +131,16 @@ int launch_expand(DeviceCtx* ctx, const void* a_packed, void* a_bytes, int rows_
 int launch_expand_weights(DeviceCtx* ctx, const void* w_packed, void* w_expanded, int n, int k, cudaStream_t stream);
 int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols, cudaStream_t stream);
 
+// Read-only streaming pass over `bytes` bytes (probe.cu): the one-launch floor of the decode shapes.
+int launch_stream_read(DeviceCtx* ctx, const void* src, size_t bytes, unsigned* sink, cudaStream_t stream);
+
 // One-off function attribute set-up (dynamic shared memory opt-in).
 int setup_tcgen05(DeviceCtx* ctx);
 int setup_tcgen05_s8(DeviceCtx* ctx);
 int setup_skinny(DeviceCtx* ctx);
+
+// Device-side status of the static-scratch entry point on the current device (no_alloc.cu).
+int poll_static_scratch_status();
 
 // Launch counter (kernels of this library launched by this process).
 void count_launch(int n = 1);
@@ -143,6 +154,7 @@ bool getenv_flag_direct_store();
 int forced_tile_n();
 int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
 int two_pass_mode();  // -1 automatic, 0 never, 1 whenever the tensor-memory family is used
+int tail_mode();  // int4_linear_set_tail: -1 automatic, 0 whole tiles only, 1 half-width items, 2 cut along K
 int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always (m > 128)
 
 }  // namespace i4l

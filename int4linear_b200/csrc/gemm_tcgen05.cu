@@ -47,7 +47,7 @@
 #include "common.h"
 #include "ptx.cuh"
 #include "epilogue.cuh"
-
+#include "schedule.cuh"
 
 namespace i4l {
 
@@ -84,6 +84,8 @@ struct Cfg {
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
+constexpr size_t kSkFlagWordsPerRegion = static_cast<size_t>(kSkMaxTiles) * 2 /*CTAs*/ * 4 /*warps*/ * 2 /*words*/;
+
 // Destination tensor maps of the gathering variant: the full Y of every rank of the node.
 constexpr int kMaxPeers = 8;
 struct PeerMaps {
@@ -97,7 +99,7 @@ __device__ __forceinline__ void
 gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_wh,
                      const CUtensorMap* y_maps, int n_y_maps, int col_shift,
                      int* __restrict__ y, int m, int n, int k,
-                     int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias,
+                     const Schedule& sched, int* status, const int* __restrict__ bias,
                      const ScaledOut& so)
 {
     constexpr int BN = C::kBN, P = C::kP, U = C::kU, CTAS = C::kCtas;
@@ -171,11 +173,9 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         if constexpr (CTAS == 2) cluster_wait();
     }
 
-    // Work items: tiles [0, split_from) as they are; each later tile as two half-width items, so
-    // that a short last wave costs half a tile time (see launch_cfg).
-    const int num_tiles = tiles_m * tiles_n;
-    const int num_items = split_from + 2 * (num_tiles - split_from);
-    const int kb_count = (k + 127) / 128;
+    // Every role walks the same list of segments (schedule.cuh): whole tiles, half-width items,
+    // K ranges of the tiles that are cut along K.
+    const int tiles_m = sched.tiles_m, tiles_n = sched.tiles_n;
     constexpr int kGroupM = 16;  // tiles of 16 consecutive M blocks share their W panel in L2
     auto tile_coord = [&](int tile, int& tm, int& tn) {
         const int group_size = kGroupM * tiles_n;
@@ -186,38 +186,26 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         tm = first_m + in_group % gm;
         tn = in_group / gm;
     };
-    // item -> tile coordinates, first column of the item inside the tile, width in columns
-    auto item_coord = [&](int item, int& tm, int& tn, int& col_off, int& width) {
-        if (item < split_from) {
-            tile_coord(item, tm, tn);
-            col_off = 0;
-            width = BN;
-        } else {
-            const int h = item - split_from;
-            tile_coord(split_from + (h >> 1), tm, tn);
-            col_off = (h & 1) * (BN / 2);
-            width = BN / 2;
-        }
-    };
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
             bool alive = true;
-            for (int item = worker; alive && item < num_items; item += workers) {
-                int tm, tn, col_off, width;
-                item_coord(item, tm, tn, col_off, width);
-                const int rows_w = width / CTAS;
-                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+            Segment sg;
+            for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si) {
+                int tm, tn;
+                tile_coord(sg.tile, tm, tn);
+                const int rows_w = sg.width / CTAS;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % P, r = it / P;
                     if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                     mbar_expect_tx(pk_full(s), C::kPreW ? C::kPkStage : (kBM + rows_w) * kBKBytes);
                     const uint32_t dst = pk_base + s * C::kPkStage;
                     tma_load_2d(dst, &tm_x, pk_full(s), kb * kBKBytes, (tm * CTAS + cta_rank) * kBM);
                     if constexpr (!C::kPreW) {
-                        tma_load_2d(dst + kBM * kBKBytes, width == BN ? &tm_w : &tm_wh, pk_full(s), kb * kBKBytes,
-                                    tn * BN + col_off + cta_rank * rows_w);
+                        tma_load_2d(dst + kBM * kBKBytes, sg.width == BN ? &tm_w : &tm_wh, pk_full(s), kb * kBKBytes,
+                                    tn * BN + sg.col_off + cta_rank * rows_w);
                     } else {
                         // Expanded W goes directly into the slot the UMMA reads; that slot is free
                         // once the UMMAs of its previous use have been committed.
@@ -237,13 +225,14 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         if (lane == 0 && cta_rank == 0) {
             uint32_t it = 0, local_tile = 0;
             bool alive = true;
-            for (int item = worker; alive && item < num_items; item += workers, ++local_tile) {
-                const uint32_t idesc = item < split_from ? umma_idesc_s8(C::kTileM, BN) : umma_idesc_s8(C::kTileM, BN / 2);
+            Segment sg;
+            for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si, ++local_tile) {
+                const uint32_t idesc = sg.width == BN ? umma_idesc_s8(C::kTileM, BN) : umma_idesc_s8(C::kTileM, BN / 2);
                 const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
                 if (!mbar_wait(tm_empty(buf), (br & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % U, r = it / U;
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
                     tc_fence_after_sync();
@@ -253,7 +242,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // 32 bytes of K per instruction: advance the start address field by 32 >> 4.
-                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb != sg.kb0 || j != 0) ? 1u : 0u);
                     }
                     if constexpr (CTAS == 2) umma_commit_2cta(up_empty(s), 3); else umma_commit(up_empty(s));
                 }
@@ -270,15 +259,20 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         uint32_t local_tile = 0;
         uint32_t chunk_no = 0;
         bool alive = true;
-        for (int item = worker; alive && item < num_items; item += workers, ++local_tile) {
-            int tm, tn, col_off, width;
-            item_coord(item, tm, tn, col_off, width);
+        Segment sg;
+        for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si, ++local_tile) {
+            int tm, tn;
+            tile_coord(sg.tile, tm, tn);
+            const int col_off = sg.col_off, width = sg.width;
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
             if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
+            // Flag pair of these 32 rows of a tile that is cut along K: [0] raised by the owner once
+            // its stores have landed, [1] counts the adders that have seen it.
+            unsigned* flag = sched.flags + ((static_cast<size_t>(sg.sk_index) * CTAS + cta_rank) * 4 + sp) * 2;
             if (so.y16 != nullptr) {
                 // Dequantised bf16 output; y_maps[0] then describes the bf16 matrix.
                 if constexpr (kTmaStore) {
@@ -286,8 +280,25 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                     else drain_accumulator_scaled_tma<false>(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
                 }
                 else drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
-            } else
-                drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
+            } else if (sg.mode == kSegAdd) {
+                // Partial sums of a tile another worker owns: wait until its stores are in place.
+                if (!flag_wait(flag, abort_flag, lane)) { alive = false; break; }
+                drain_accumulator<kTmaStore, true>(t_addr, width, row0, col0, m, n, y, nullptr, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
+                if (lane == 0 && atomicAdd(flag + 1, 1u) == static_cast<unsigned>(sg.adders - 1)) {
+                    // Every adder of these rows has passed its wait: leave the pair clean for the next launch.
+                    flag[0] = 0;
+                    flag[1] = 0;
+                }
+            } else {
+                drain_accumulator<kTmaStore, false>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
+                if (sg.mode == kSegOwner) {
+                    if (lane == 0) {
+                        if constexpr (kTmaStore) tma_store_wait_all<0>();  // the stores have been performed, not just read
+                        flag_raise(flag);
+                    }
+                    __syncwarp();
+                }
+            }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -314,10 +325,11 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         // The pair's barrier completes long before the first TMA data arrives, so waiting for it
         // here (warp still convergent) costs nothing.
         if constexpr (CTAS == 2) cluster_wait();
-        for (int item = worker; alive && item < num_items; item += workers) {
+        Segment sg;
+        for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si) {
             // 16-byte chunks to convert in this item's stages (a half-width item has fewer W rows)
-            const int chunks = C::kPreW ? kChunks : (item < split_from ? kChunks : (kBM + C::kRowsW / 2) * 4);
-            for (int kb = 0; kb < kb_count; ++kb, ++it) {
+            const int chunks = C::kPreW ? kChunks : (sg.width == BN ? kChunks : (kBM + C::kRowsW / 2) * 4);
+            for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
@@ -385,11 +397,10 @@ gemm_s4_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
                        const __grid_constant__ CUtensorMap tm_wh,
                        const __grid_constant__ CUtensorMap tm_y,
                        int* __restrict__ y, int m, int n, int k,
-                       int tiles_m, int tiles_n, int split_from, int* status, const int* __restrict__ bias,
+                       const Schedule sched, int* status, const int* __restrict__ bias,
                        const ScaledOut so)
 {
-    gemm_s4_tcgen05_body<C, kTmaStore>(tm_x, tm_w, tm_wh, &tm_y, 1, 0, y, m, n, k, tiles_m, tiles_n, split_from,
-                                       status, bias, so);
+    gemm_s4_tcgen05_body<C, kTmaStore>(tm_x, tm_w, tm_wh, &tm_y, 1, 0, y, m, n, k, sched, status, bias, so);
 }
 
 // GEMM fused with the all-gather of its result: the epilogue stores this rank's column block of Y
@@ -402,11 +413,11 @@ gemm_s4_tcgen05_gather_kernel(const __grid_constant__ CUtensorMap tm_x,
                               const __grid_constant__ CUtensorMap tm_w,
                               const __grid_constant__ CUtensorMap tm_wh,
                               const __grid_constant__ PeerMaps peers, int n_peers, int col_shift,
-                              int m, int n, int k, int tiles_m, int tiles_n, int split_from, int* status,
+                              int m, int n, int k, const Schedule sched, int* status,
                               const int* __restrict__ bias)
 {
-    gemm_s4_tcgen05_body<C, true>(tm_x, tm_w, tm_wh, peers.map, n_peers, col_shift, nullptr, m, n, k, tiles_m, tiles_n,
-                                  split_from, status, bias, ScaledOut{});
+    gemm_s4_tcgen05_body<C, true>(tm_x, tm_w, tm_wh, peers.map, n_peers, col_shift, nullptr, m, n, k, sched,
+                                  status, bias, ScaledOut{});
 }
 
 using Cfg256 = Cfg<256, 3, 2, 1>;
@@ -415,17 +426,6 @@ using Cfg64 = Cfg<64, 4, 4, 1>;
 using Cfg256x2 = Cfg<256, 4, 4, 2>;  // 256 x 256 tile on a CTA pair (a fourth expanded slot is worth 4 %)
 using Cfg256x2W = Cfg<256, 4, 4, 2, true>;  // the same with pre-expanded weights
 using Cfg128W = Cfg<128, 4, 4, 1, true>;
-
-// Experiment knob INT4L_TAIL_SPLIT=0 turns the half-width tail items off.
-bool tail_split_enabled()
-{
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("INT4L_TAIL_SPLIT");
-        v = (e && atoi(e) == 0) ? 0 : 1;
-    }
-    return v != 0;
-}
 
 template <class C, bool kTmaStore>
 int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const GatherDst* gather = nullptr)
@@ -450,22 +450,25 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     } else {
         tm_y = tm_x;  // unused by the kernel
     }
+    // The last, partial wave of tiles: cut along K where partial sums can be added into Y (int32
+    // output on this GPU), else as half-width items, else left as whole tiles (schedule.cuh).
     const int max_workers = C::kCtas == 2 ? ctx->max_pairs : ctx->sm_count;
-    const int num_tiles = tiles_m * tiles_n;
-    // Tail splitting: with a static round-robin schedule a last wave that fills at most half of
-    // the workers still costs a whole tile time.  Its tiles are then issued as two half-width items
-    // each, which halves that cost (4096^2 outputs on 74 CTA pairs: 3.5 instead of 4 tile times).
-    int split_from = num_tiles;
-    tm_wh = tm_x;  // unused unless tiles are split
-    if (!C::kPreW && C::kCtas == 2 && tail_split_enabled()) {
-        const int rem = num_tiles % max_workers;
-        if (rem > 0 && 2 * rem <= max_workers) {
-            split_from = num_tiles - rem;
-            rc = make_tensor_map_2d(ctx, &tm_wh, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW / 2, false);
-            if (rc != INT4L_OK) return rc;
-        }
+    const int tail = tail_mode();
+    const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr && gather == nullptr && ctx->sk_flags != nullptr;
+    const bool can_halve = (tail < 0 || tail == 1) && !C::kPreW && C::kCtas == 2;
+    Schedule sched = plan_schedule(tiles_m, tiles_n, (p.k + 127) / 128, max_workers, can_add, can_halve);
+    tm_wh = tm_x;  // unused unless tiles are halved
+    if (sched.half_tiles > 0) {
+        rc = make_tensor_map_2d(ctx, &tm_wh, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW / 2, false);
+        if (rc != INT4L_OK) return rc;
     }
-    const int workers = min(split_from + 2 * (num_tiles - split_from), max_workers);
+    if (sched.sk_tiles > 0) {
+        // Launches take the flag sets in turn, so launches that overlap in time (different
+        // streams) do not share one unless kSkRegions of them are in flight at once.
+        const unsigned long long turn = ctx->sk_launches.fetch_add(1);
+        sched.flags = ctx->sk_flags + (turn % kSkRegions) * kSkFlagWordsPerRegion;
+    }
+    const int workers = sched.workers;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(workers * C::kCtas, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
@@ -489,15 +492,14 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
             }
             for (int d = gather->world; d < kMaxPeers; ++d) peers.map[d] = peers.map[0];
             e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_gather_kernel<C>, tm_x, tm_w, tm_wh, peers, gather->world,
-                                   gather->col_offset, p.m, p.n, p.k, tiles_m, tiles_n, split_from, ctx->status_dev, p.bias);
+                                   gather->col_offset, p.m, p.n, p.k, sched, ctx->status_dev, p.bias);
             count_launch();
             if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
             return INT4L_OK;
         }
     }
     e = cudaLaunchKernelEx(&cfg, gemm_s4_tcgen05_kernel<C, kTmaStore>, tm_x, tm_w, tm_wh, tm_y,
-                           static_cast<int*>(p.y), p.m, p.n, p.k, tiles_m, tiles_n, split_from,
-                           ctx->status_dev, p.bias, p.scaled);
+                           static_cast<int*>(p.y), p.m, p.n, p.k, sched, ctx->status_dev, p.bias, p.scaled);
     count_launch();
     if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
     return INT4L_OK;
@@ -548,6 +550,15 @@ int setup_tcgen05(DeviceCtx* ctx)
         pairs = ctx->sm_count / 2;
     }
     ctx->max_pairs = pairs < ctx->sm_count / 2 ? pairs : ctx->sm_count / 2;
+    // Flags of the tiles that are cut along K (schedule.cuh): all zero between launches.
+    const size_t flag_bytes = kSkRegions * kSkFlagWordsPerRegion * sizeof(unsigned);
+    void* flags = nullptr;
+    if (cudaMalloc(&flags, flag_bytes) != cudaSuccess || cudaMemset(flags, 0, flag_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return INT4L_ERR_CUDA;
+    }
+    ctx->sk_flags = static_cast<unsigned*>(flags);
+    ctx->sk_flag_bytes = flag_bytes;
     return INT4L_OK;
 }
 
@@ -570,20 +581,23 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
     // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile
     // re-expands X less often per output, a narrower one fills more SMs when the problem is small.
-    const long long tiles_m = (p.m + kBM - 1) / kBM;
-    auto tiles = [&](int bn) { return tiles_m * ((p.n + bn - 1) / bn); };
-    auto whole_waves = [](long long t, int workers) { return static_cast<double>((t + workers - 1) / workers); };
-    const long long pair_tiles = ((p.m + 255) / 256) * static_cast<long long>((p.n + 255) / 256);
-    // pairs: the last wave may run as half-width items (tail splitting), hence half-wave steps
-    const double pair_waves = pair_tiles <= ctx->max_pairs
-                                  ? 1.0
-                                  : static_cast<double>((2 * pair_tiles + ctx->max_pairs - 1) / ctx->max_pairs) / 2.0;
-    const double cost_pairs = p.m > 128 ? pair_waves * 1.0 : 1e30;  // a lone row block would leave CTA 1 idle
+    // The schedule's own estimate of the busiest worker's time (whole waves plus the K-cut or
+    // half-width tail) stands in for the wave count.
+    const int kb_count = (p.k + 127) / 128;
+    const int tail = tail_mode();
+    const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr && ctx->sk_flags != nullptr;
+    auto waves = [&](int tile_m, int bn, int workers, bool can_halve) {
+        double c = 0.0;
+        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, kb_count, workers, can_add, can_halve, &c);
+        return c;
+    };
+    const double cost_pairs = p.m > 128 ? waves(256, 256, ctx->max_pairs, tail < 0 || tail == 1)
+                                        : 1e30;  // a lone row block would leave CTA 1 idle
     // Tile times relative to the pair tile, from CUDA-graph replays (no launch overhead in the
     // figures) at K = 1024 and 4096: 128 x 256 on one CTA 1.7, 128 x 128 1.1, 128 x 64 0.9.
-    const double cost256 = whole_waves(tiles(256), ctx->sm_count) * 1.7;
-    const double cost128 = whole_waves(tiles(128), ctx->sm_count) * 1.1;
-    const double cost64 = whole_waves(tiles(64), ctx->sm_count) * 0.9;
+    const double cost256 = waves(kBM, 256, ctx->sm_count, false) * 1.7;
+    const double cost128 = waves(kBM, 128, ctx->sm_count, false) * 1.1;
+    const double cost64 = waves(kBM, 64, ctx->sm_count, false) * 0.9;
     int bn = 256;
     double best = cost256;
     if (cost128 < best) { best = cost128; bn = 128; }

@@ -256,10 +256,30 @@ int set_attr_s8()
 
 }  // namespace
 
-int setup_tcgen05_s8(DeviceCtx*)
+int setup_tcgen05_s8(DeviceCtx* ctx)
 {
     int rc = set_attr_s8<CfgS8Pair>();
     if (rc == INT4L_OK) rc = set_attr_s8<CfgS8One>();
+    if (rc != INT4L_OK || ctx->max_pairs > 0) return rc;
+    // A context that has not learnt yet how many CTA pairs the device holds at once (the
+    // static-scratch entry point builds its own) asks for this kernel's figure.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * ctx->sm_count, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = CfgS8Pair::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int pairs = 0;
+    if (cudaOccupancyMaxActiveClusters(&pairs, gemm_s8_tcgen05_kernel<CfgS8Pair, true>, &cfg) != cudaSuccess || pairs <= 0) {
+        cudaGetLastError();
+        pairs = ctx->sm_count / 2;
+    }
+    ctx->max_pairs = pairs < ctx->sm_count / 2 ? pairs : ctx->sm_count / 2;
     return rc;
 }
 

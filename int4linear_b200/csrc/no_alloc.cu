@@ -20,6 +20,10 @@
 // stream capture starts on that device.  No call here, first or later, uses cudaMalloc,
 // cudaFree, cudaHostAlloc or any other allocating routine.
 //
+// A bounded wait that expires inside these kernels raises a status word that also lives in the
+// library's device image; int4_linear_last_status() fetches and clears it with a symbol copy (no
+// allocation either), so a device-side timeout here is reported like one of the regular path.
+//
 // All calls on a device share the one array, and it still holds whatever the previous call
 // left there.  Nothing in it needs to start at zero: the pre-pass overwrites every byte the GEMM
 // then reads.  Two calls whose kernels can run at the same time on one device (different
@@ -83,7 +87,7 @@ StaticCtx* static_ctx(int* status)
     }
     s->ctx.device = dev;
     s->ctx.sm_count = prop.multiProcessorCount;
-    s->ctx.max_pairs = prop.multiProcessorCount / 2;
+    s->ctx.max_pairs = 0;  // setup_tcgen05_s8 fills it in from an occupancy query
     s->ctx.cc_major = prop.major;
     s->ctx.cc_minor = prop.minor;
     s->ctx.status_dev = static_cast<int*>(status_word);
@@ -97,6 +101,29 @@ StaticCtx* static_ctx(int* status)
 }
 
 }  // namespace
+
+namespace i4l {
+
+// Status word of the static-scratch kernels on the current device: fetched from the device image
+// and cleared when set.  INT4L_OK when this entry point has never run on the device.
+int poll_static_scratch_status()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return INT4L_OK; }
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static[dev].ready) return INT4L_OK;
+    }
+    int word = INT4L_OK;
+    if (cudaMemcpyFromSymbol(&word, g_static_status, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
+    if (word != INT4L_OK) {
+        const int zero = INT4L_OK;
+        if (cudaMemcpyToSymbol(g_static_status, &zero, sizeof(int)) != cudaSuccess) cudaGetLastError();
+    }
+    return word;
+}
+
+}  // namespace i4l
 
 extern "C" int int4_linear_launch_static_scratch_async(const void* x_packed_d, const void* w_packed_d,
                                                        const int* bias_d, void* y_d, int m, int n, int k,

@@ -205,6 +205,29 @@ def linear_prepared(x_packed, w_expanded, out=None, bias=None, stream=None):
     return out
 
 
+def linear_expanded(x_expanded, w_expanded, out=None, bias=None, stream=None):
+    """Y = X @ W^T (+ bias) with BOTH operands already expanded by prepare_weights ([m, k] and
+    [n, k] uint8): the pure 8-bit GEMM of the two-pass path (asynchronous)."""
+    import torch
+    m, k = x_expanded.shape
+    n = w_expanded.shape[0]
+    for t in (x_expanded, w_expanded):
+        if t.dtype != torch.uint8 or not t.is_contiguous() or t.shape[1] != k or not t.is_cuda:
+            raise ValueError("operands must be contiguous CUDA uint8 tensors [rows, k] made by prepare_weights")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.int32, device=x_expanded.device)
+    elif tuple(out.shape) != (m, n) or out.dtype != torch.int32 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int32 tensor of shape [m, n]")
+    handle = (stream or torch.cuda.current_stream(x_expanded.device)).cuda_stream
+    with torch.cuda.device(x_expanded.device):
+        st = _lib.load().int4_linear_launch_expanded_async(
+            x_expanded.data_ptr(), w_expanded.data_ptr(), bias.data_ptr() if bias is not None else None,
+            out.data_ptr(), m, n, k, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_launch_expanded_async")
+    return out
+
+
 def linear_host(x_packed: np.ndarray, w_packed: np.ndarray, k: int, out: np.ndarray | None = None,
                 w_resident: bool = False) -> np.ndarray:
     """The whole host-side sequence of the reference's correctness program
@@ -248,6 +271,13 @@ def set_two_pass(mode: int) -> int:
     if st != 0:
         raise Int4LinearError(st, "int4_linear_set_two_pass")
     return st
+
+
+def set_tail(mode: int) -> None:
+    """-1 automatic, 0 whole tiles, 1 half-width items, 2 last wave cut along K (int4_linear_set_tail)."""
+    st = _lib.load().int4_linear_set_tail(mode)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_set_tail")
 
 
 def set_overlap(mode: int) -> int:

@@ -21,7 +21,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    for (m, n, k) in [(512, 1024, 512), (96, 2048, 1024), (1000, 1536, 256), (300, 1000, 256)]:  # the last: ragged N, NCCL fallback
+    for (m, n, k) in [(512, 1024, 512), (96, 2048, 1024), (1000, 1536, 256), (300, 1000, 256),  # ragged N: NCCL fallback
+                      (64, 256, 128)]:  # fewer 256-row units than ranks: the last rank owns nothing
         sh = shard_bounds(n, world, rank)
         x, w = L.uniform_s4(0x7A01, m, k), L.uniform_s4(0x7A02, n, k)
         xp, wp = L.pack_bytes(x), L.pack_bytes(w)

@@ -20,3 +20,18 @@ def test_reference_arm_prints_one_json_line():
     assert d["cpu_baseline"]["kind"] in ("reference", "port") and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
     assert d["config"]["workload"].startswith("c1")
+    assert d["scaling"] == "strong" and d["metric"].endswith("M=1024 N=1024 K=1024")
+    assert set(d["config"]) == {"workload", "shard", "l2", "variant"}
+
+
+def test_both_arms_describe_the_same_work():
+    """The reference arm and this library's arm build `metric` and `config` with the same two
+    functions, from the problem that is actually computed at that number of GPUs."""
+    sys.path.insert(0, ROOT)
+    import bench
+    assert bench.metric_name("m8", 8, "strong") == "INT4 GEMM TOPS at M=8192 N=8192 K=8192"
+    assert bench.metric_name("m8", 8, "weak") == "INT4 GEMM TOPS at M=8192 N=65536 K=8192"
+    c = bench.describe_config("m8", 8, "strong")
+    assert c["workload"] == "m8: M=8192 N=8192 K=8192" and c["shard"].startswith("8 x (M=8192, N=1024, K=8192)")
+    assert bench.describe_config("c5", 8, "strong")["shard"].startswith("8 x (M=8192, N=3584, K=8192)")
+    assert bench.metric_name("c4", 1, "strong").startswith("INT4 GEMM achieved HBM GB/s")

@@ -405,3 +405,31 @@ def test_concurrent_host_threads_on_their_own_streams(cuda):
         t.join()
     assert not errors, errors
     assert L.last_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 256), (1024, 1024, 1024), (64, 72, 96)], ids=lambda s: "x".join(map(str, s)))
+def test_both_operands_pre_expanded(cuda, shape):
+    """int4_linear_launch_expanded_async: X and W expanded once by the prepare call, then the
+    pure 8-bit GEMM; same bits as the packed path."""
+    import torch
+    m, n, k = shape
+    x, w, xp, wp = make_case(m, n, k, seed=31)
+    xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+    xe, we = L.prepare_weights(xd), L.prepare_weights(wd)
+    assert xe.shape == (m, k) and we.shape == (n, k)
+    y = L.linear_expanded(xe, we)
+    torch.cuda.synchronize()
+    assert L.last_status() == 0
+    assert O.is_same(y.cpu().numpy(), O.linear_ref(x.astype(np.int32), w.astype(np.int32)))
+
+
+def test_empty_shard_returns_an_empty_result(cuda):
+    """A rank whose shard of W has no rows (more ranks than 256-row units) gets an [m, 0] result
+    and launches nothing."""
+    import torch
+    xd = torch.zeros((64, 64), dtype=torch.uint8, device=cuda)
+    wd = torch.zeros((0, 64), dtype=torch.uint8, device=cuda)
+    before = L.launch_count()
+    y = L.linear(xd, wd)
+    assert tuple(y.shape) == (64, 0) and y.dtype == torch.int32
+    assert L.launch_count() == before

@@ -135,3 +135,36 @@ def test_no_gpu_means_error_not_fallback():
     with pytest.raises(L.Int4LinearError) as e:
         L.linear_host(x, x, 32)
     assert e.value.status == 6
+
+
+def test_tile_schedule_covers_every_k_block_once(tmp_path):
+    """The schedule of the persistent GEMM kernels (whole tiles, half-width items, tiles cut along
+    K) is plain host/device arithmetic: tests/schedule_check.cpp enumerates it for tens of thousands
+    of (tiles, K blocks, workers) combinations with the host compiler."""
+    import subprocess
+    exe = str(tmp_path / "schedule_check")
+    subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, os.path.join(ROOT, "tests", "schedule_check.cpp")], check=True)
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "SCHEDULE_OK" in out.stdout, out.stdout + out.stderr
+
+
+def test_numa_binding_reads_sysfs_and_keeps_to_allowed_cpus(tmp_path):
+    from int4linear_b200 import numa
+    assert numa.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("48-95\n")
+    got = []
+    r = numa.bind_to_gpu_node("0000:1B:00.0", sysfs=str(tmp_path), setaffinity=got.append, allowed=set(range(40, 60)))
+    assert r == {"node": 1, "cpus": 12, "bound": True} and got == [set(range(48, 60))]
+    # no NUMA information (containers often report -1), an unknown device, no usable CPU: nothing is changed
+    (dev / "numa_node").write_text("-1\n")
+    got.clear()
+    assert numa.bind_to_gpu_node("0000:1b:00.0", sysfs=str(tmp_path), setaffinity=got.append)["bound"] is False
+    assert numa.bind_to_gpu_node("0000:ff:00.0", sysfs=str(tmp_path), setaffinity=got.append)["bound"] is False
+    (dev / "numa_node").write_text("1\n")
+    assert numa.bind_to_gpu_node("0000:1b:00.0", sysfs=str(tmp_path), setaffinity=got.append, allowed={1, 2})["bound"] is False
+    assert got == []

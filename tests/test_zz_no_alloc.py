@@ -5,9 +5,10 @@ device memory to another allocator, or may not stall on the synchronisation an a
 implies.  For them the two-pass operator exists in a form whose scratch is a fixed array inside
 the library.  This file checks, through the C ABI, that it returns exactly what the regular entry
 point returns, on two consecutive calls (the second finds the first call's bytes still in the
-shared scratch), that it refuses shapes beyond its fixed capacity, and that it works both as the
-very first thing a fresh process does with the library and after every other test (the file name
-makes pytest collect it last).
+shared scratch); that it accepts and computes a problem that fills the array to the last byte and
+refuses anything larger; that its status word is read back by int4_linear_last_status; and that
+it works when it is the very first call a fresh process makes into the library (a child process)
+as well as after every other test (the file name makes pytest collect it last).
 """
 import ctypes
 
@@ -63,7 +64,63 @@ def test_static_scratch_rejects_what_does_not_fit(cuda):
     # (m + n) * k = 16384 * 8192 = 128 Mi > 64 Mi: refused before anything is launched
     assert lib.int4_linear_launch_static_scratch_async(p, p, None, p, 8192, 8192, 8192, None) == 7
     assert lib.int4_linear_status_string(7).decode().startswith("size beyond")
-    # exactly at the limit the size check passes (64 Mi) -- only checked, not run: pointers are dummies
+    # one K step beyond the capacity: (8192 + 8192) * 4128 > 64 Mi
     assert lib.int4_linear_launch_static_scratch_async(p, p, None, p, 8192, 8192, 4096 + 32, None) == 7
     assert lib.int4_linear_launch_static_scratch_async(None, p, None, p, 8, 8, 32, None) == 1
     assert lib.int4_linear_launch_static_scratch_async(p, p, None, p, 8, 8, 40, None) == 2
+
+
+def test_static_scratch_exactly_at_capacity(cuda):
+    """(m + n) * k = (8192 + 8192) * 4096 = 67 108 864 bytes: the whole array, to the last byte."""
+    import torch
+    lib = _lib.load()
+    m = n = 8192
+    k = 4096
+    xd = torch.from_numpy(L.uniform_s4_packed(0xA0C1, m, k)).to(cuda)
+    wd = torch.from_numpy(L.uniform_s4_packed(0xB0C1, n, k)).to(cuda)
+    want = torch.empty((m, n), dtype=torch.int32, device=cuda)
+    got = torch.full((m, n), -2, dtype=torch.int32, device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.int4_linear_launch_async(xd.data_ptr(), wd.data_ptr(), want.data_ptr(), m, n, k, stream) == 0
+    assert _call_static(lib, xd, wd, got, m, n, k) == 0
+    torch.cuda.synchronize()
+    assert lib.int4_linear_last_status() == 0   # polls the regular AND the static-scratch status word
+    assert torch.equal(got, want)
+
+
+_CHILD = r"""
+import sys
+import numpy as np
+import torch
+sys.path.insert(0, sys.argv[1])
+from int4linear_b200 import _lib, uniform_s4, pack_bytes
+torch.cuda.set_device(0)
+dev = torch.device("cuda:0")
+m, n, k = 300, 520, 512
+x, w = uniform_s4(0xA0C2, m, k), uniform_s4(0xB0C2, n, k)
+xd, wd = torch.from_numpy(pack_bytes(x)).to(dev), torch.from_numpy(pack_bytes(w)).to(dev)
+got = torch.full((m, n), -2, dtype=torch.int32, device=dev)
+want = torch.full((m, n), -1, dtype=torch.int32, device=dev)
+lib = _lib.load()
+assert lib.int4_linear_launch_count() == 0
+# the first call this process makes into the library
+st = lib.int4_linear_launch_static_scratch_async(xd.data_ptr(), wd.data_ptr(), None, got.data_ptr(), m, n, k, None)
+assert st == 0, st
+torch.cuda.synchronize()
+assert lib.int4_linear_last_status() == 0
+assert lib.int4_linear_launch_async(xd.data_ptr(), wd.data_ptr(), want.data_ptr(), m, n, k, None) == 0
+torch.cuda.synchronize()
+assert torch.equal(got, want)
+assert np.array_equal(got.cpu().numpy(), (x.astype(np.int64) @ w.astype(np.int64).T).astype(np.int32))
+print("STATIC_FIRST_OK")
+"""
+
+
+def test_static_scratch_as_first_call_of_a_fresh_process(cuda):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", _CHILD, root], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "STATIC_FIRST_OK" in out.stdout
