@@ -235,11 +235,13 @@ def measure_int8_peak(torch, L, dev, launches=10):
     library's own byte GEMM (TMA -> tcgen05.mma kind::i8, no unpack stage).  Measurement only:
     neither is on the operator's path."""
     n = 8192
-    out = {"shape": f"M=N=K={n}", "launches": launches}
+    out = {"shape": f"M=N=K={n}", "launches": launches,
+           "data": "bytes = 16 x uniform s4, i.e. exactly what the operator's tensor-core stage multiplies "
+                   "(a part at its power limit runs full-range random bytes slower; that figure is given too)"}
     g = torch.Generator(device=dev)
     g.manual_seed(0x18)
-    a = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev, generator=g)
-    b = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev, generator=g)
+    a = (torch.randint(-8, 8, (n, n), dtype=torch.int8, device=dev, generator=g) * 16).contiguous()
+    b = (torch.randint(-8, 8, (n, n), dtype=torch.int8, device=dev, generator=g) * 16).contiguous()
     ops = 2.0 * n * n * n
 
     def best(fn):
@@ -269,7 +271,15 @@ def measure_int8_peak(torch, L, dev, launches=10):
     except Exception as e:
         out["own_byte_gemm_tops"] = None
         out["own_byte_gemm_error"] = repr(e)[:160]
-    cands = [v for v in (out["library_int8_gemm_tops"], out["own_byte_gemm_tops"]) if v]
+    try:
+        a2 = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev, generator=g)
+        b2 = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev, generator=g)
+        b2t = b2.t()
+        out["library_int8_gemm_tops_full_range_bytes"] = best(lambda: torch._int_mm(a2, b2t))
+    except Exception:
+        out["library_int8_gemm_tops_full_range_bytes"] = None
+    cands = [v for v in (out["library_int8_gemm_tops"], out["own_byte_gemm_tops"],
+                         out["library_int8_gemm_tops_full_range_bytes"]) if v]
     out["peak_tops"] = max(cands) if cands else None
     return out
 
@@ -360,6 +370,27 @@ def quick_config(torch, L, dev, flush, name, int8_peak, hbm_peak, launches=5):
             out["read_only_floor"] = {"ms": fms, "gbs": (n * k // 2) / (fms * 1e-3) / 1e9,
                                       "note": "one launch of a read-only streaming kernel over the same W bytes"}
     if bound == "tensor":
+        # for scale: a library int8 GEMM of the same shape on resident bytes (measurement only)
+        try:
+            g = torch.Generator(device=dev)
+            g.manual_seed(0x19)
+            a8 = (torch.randint(-8, 8, (m, k), dtype=torch.int8, device=dev, generator=g) * 16).contiguous()
+            b8 = (torch.randint(-8, 8, (n, k), dtype=torch.int8, device=dev, generator=g) * 16).contiguous().t()
+            for _ in range(2):
+                torch._int_mm(a8, b8)
+            ls = []
+            for _ in range(launches):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch._int_mm(a8, b8)
+                e1.record()
+                torch.cuda.synchronize()
+                ls.append(e0.elapsed_time(e1))
+            out["library_int8_gemm_same_shape_tops"] = ops / (statistics.median(ls) * 1e-3) / 1e12
+            del a8, b8
+        except Exception as e:
+            out["library_int8_gemm_same_shape_tops"] = None
         tops = ops / (best_ms * 1e-3) / 1e12
         out["tops"] = tops
         out["frac_of_measured_int8_peak"] = tops / int8_peak if int8_peak else None

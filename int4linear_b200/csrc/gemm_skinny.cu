@@ -181,19 +181,20 @@ gemm_s4_skinny_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__
 
 
 // Register-resident variant for m <= 16 and K <= 8192 (the decode shape proper).
-// Each of the 16 warps owns a fixed slice of K (KBW blocks of 128 elements) for every
+// Each warp (16 or 32 per CTA) owns a fixed slice of K (KBW blocks of 128 elements) for every
 // W group of the CTA, so its X fragments are loaded and expanded ONCE into registers and
 // the inner loop is nothing but: one 16-byte streaming load per lane and K block, eight
 // ALU operations to expand it, four MMAs.  Weight loads for several groups ahead are kept
 // in flight, and the first of them are issued before anything else happens in the kernel,
 // so HBM is busy from the first cycle; X never goes through shared memory.
-template <int KBW, int D, int MINB>
-__global__ void __launch_bounds__(kSkinnyThreads, MINB)
+template <int KBW, int D, int MINB, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ w, int* __restrict__ y,
                           int m, int n, int k, int groups_total, int overlap, const int* __restrict__ bias,
                           const ScaledOut so)
 {
-    // D = groups of weight loads in flight per warp.
+    // D = groups of weight loads in flight per warp; WARPS * KBW K blocks are covered by one CTA.
+    constexpr int kThreadsHere = WARPS * 32;
     // overlap: 0 = ordinary launch.  1, 2 = launched with programmatic stream serialisation:
     // this grid may start while the preceding work in the stream is still running, and lets its
     // own successor do the same.  Everything it reads before griddepcontrol.wait must therefore
@@ -230,8 +231,10 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
 
     if (overlap == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // X fragments of this warp's K slice: rows g and g + 8, expanded to bytes.
-    uint32_t a[KBW][4][4];
+    // X words of this warp's K slice, rows g and g + 8, kept PACKED (two registers per MMA): the
+    // nibble expansion is redone for every group -- six ALU operations per MMA -- because the
+    // registers this saves hold weight loads in flight, which is what the kernel's speed hangs on.
+    uint32_t xa[KBW][4], xb[KBW][4];
 #pragma unroll
     for (int u = 0; u < KBW; ++u) {
         uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
@@ -239,18 +242,11 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
             if (g < m) x0 = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(g) * row_bytes + col0 + u * 64);
             if (g + 8 < m) x1 = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(g + 8) * row_bytes + col0 + u * 64);
         }
-        const uint32_t r0[4] = {x0.x, x0.y, x0.z, x0.w};
-        const uint32_t r1[4] = {x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            a[u][e][0] = (r0[e] << 4) & 0xF0F0F0F0u;
-            a[u][e][1] = (r1[e] << 4) & 0xF0F0F0F0u;
-            a[u][e][2] = r0[e] & 0xF0F0F0F0u;
-            a[u][e][3] = r1[e] & 0xF0F0F0F0u;
-        }
+        xa[u][0] = x0.x; xa[u][1] = x0.y; xa[u][2] = x0.z; xa[u][3] = x0.w;
+        xb[u][0] = x1.x; xb[u][1] = x1.y; xb[u][2] = x1.z; xb[u][3] = x1.w;
     }
 
-    for (int i = tid; i < n_groups * 128; i += kSkinnyThreads) acc[i] = 0;
+    for (int i = tid; i < n_groups * 128; i += kThreadsHere) acc[i] = 0;
     __syncthreads();
 
     for (int gi0 = 0; gi0 < n_groups; gi0 += D) {
@@ -264,7 +260,8 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
                     const uint32_t ww[4] = {wv[d][u].x, wv[d][u].y, wv[d][u].z, wv[d][u].w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
-                        mma_s8(c, a[u][e][0], a[u][e][1], a[u][e][2], a[u][e][3],
+                        mma_s8(c, (xa[u][e] << 4) & 0xF0F0F0F0u, (xb[u][e] << 4) & 0xF0F0F0F0u,
+                               xa[u][e] & 0xF0F0F0F0u, xb[u][e] & 0xF0F0F0F0u,
                                (ww[e] << 4) & 0xF0F0F0F0u, ww[e] & 0xF0F0F0F0u);
                 }
                 load_group(gi + D, wv[d]);
@@ -281,7 +278,7 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
     if (overlap == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int cols = n_groups * 8;
     const int col_base = g_begin * 8;
-    for (int i = tid; i < m * cols; i += kSkinnyThreads) {
+    for (int i = tid; i < m * cols; i += kThreadsHere) {
         const int r = i / cols, cc = i - r * cols;
         const int col = col_base + cc;
         if (col < n) write_out(y, bias, so, r, col, n, acc[((cc >> 3) * 16 + r) * 8 + (cc & 7)]);
@@ -425,14 +422,18 @@ gemm_s4_skinny_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const uint8_
 // launch lasts microseconds; a getenv per launch would show):
 //   INT4L_SKINNY_CTAS_PER_SM = 1 | 2   CTAs per SM of the register variant
 //   INT4L_SKINNY_ROWS / INT4L_SKINNY_BUFS   stage geometry of the TMA variant
+//   INT4L_SKINNY_DEPTH   groups of weight loads in flight per warp of the register variant
+//   INT4L_SKINNY_EVEN_GRID = 0   grid = all CTA slots instead of equal shares per CTA
 struct SkinnyEnv {
-    int ctas_per_sm = 0, stage_rows = 0, n_buffers = 2;
+    int ctas_per_sm = 0, stage_rows = 0, n_buffers = 2, depth = 0, even_grid = 1;
 };
 const SkinnyEnv& skinny_env()
 {
     static const SkinnyEnv env = [] {
         SkinnyEnv v;
         if (const char* e = getenv("INT4L_SKINNY_CTAS_PER_SM")) v.ctas_per_sm = atoi(e) == 1 ? 1 : 2;
+        if (const char* e = getenv("INT4L_SKINNY_DEPTH")) v.depth = atoi(e);
+        if (const char* e = getenv("INT4L_SKINNY_EVEN_GRID")) v.even_grid = atoi(e);
         if (const char* e = getenv("INT4L_SKINNY_ROWS")) {
             v.stage_rows = atoi(e);
             if (const char* b = getenv("INT4L_SKINNY_BUFS")) v.n_buffers = atoi(b);
@@ -481,6 +482,31 @@ bool plan_skinny(const DeviceCtx* ctx, const Problem& p, SkinnyPlan* out)
 
 }  // namespace
 
+template <int KBW, int D, int MINB, int WARPS>
+cudaError_t reg_attr()
+{
+    return cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<KBW, D, MINB, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+}
+
+template <int KBW, int D, int MINB, int WARPS>
+cudaError_t reg_launch(cudaLaunchConfig_t cfg, int slots_per_sm_cap, const DeviceCtx* ctx, const Problem& p, int groups_total, int overlap,
+                       bool even_grid)
+{
+    // Every CTA gets the same number of 8-row groups (the last one possibly fewer): the launch
+    // lasts as long as its busiest CTA, and one group more or less is a sixth of the work.
+    const int slots = (MINB < slots_per_sm_cap ? MINB : slots_per_sm_cap) * ctx->sm_count;
+    const int per_cta = (groups_total + slots - 1) / slots;
+    int grid = (groups_total + per_cta - 1) / per_cta;
+    if (!even_grid) grid = groups_total < slots ? groups_total : slots;
+    const int per_cta_max = (groups_total + grid - 1) / grid;
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(per_cta_max) * 128 * sizeof(int);
+    return cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<KBW, D, MINB, WARPS>, static_cast<const uint8_t*>(p.x),
+                              static_cast<const uint8_t*>(p.w), static_cast<int*>(p.y), p.m, p.n, p.k, groups_total, overlap,
+                              p.bias, p.scaled);
+}
+
 bool skinny_supports(const DeviceCtx* ctx, const Problem& p)
 {
     SkinnyPlan s;
@@ -493,9 +519,14 @@ int setup_skinny(DeviceCtx*)
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<1, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<2, 2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_s4_skinny_reg_kernel<4, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e == cudaSuccess) e = reg_attr<1, 4, 2, 16>();
+    if (e == cudaSuccess) e = reg_attr<1, 8, 2, 16>();
+    if (e == cudaSuccess) e = reg_attr<2, 2, 2, 16>();
+    if (e == cudaSuccess) e = reg_attr<2, 3, 2, 16>();
+    if (e == cudaSuccess) e = reg_attr<1, 8, 1, 32>();
+    if (e == cudaSuccess) e = reg_attr<1, 6, 1, 32>();
+    if (e == cudaSuccess) e = reg_attr<2, 3, 1, 32>();
+    if (e == cudaSuccess) e = reg_attr<4, 2, 1, 16>();
     return e == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }
 
@@ -515,25 +546,28 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         // otherwise two, which hides more latency inside a single launch.
         int ctas_per_sm = overlap == 2 ? 1 : 2;
         if (skinny_env().ctas_per_sm) ctas_per_sm = skinny_env().ctas_per_sm;
-        const int grid = s.groups_total < ctas_per_sm * ctx->sm_count ? s.groups_total : ctas_per_sm * ctx->sm_count;
-        const int per_cta = (s.groups_total + grid - 1) / grid;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid, 1, 1);
-        cfg.blockDim = dim3(kSkinnyThreads, 1, 1);
-        cfg.dynamicSmemBytes = static_cast<size_t>(per_cta) * 128 * sizeof(int);
         cfg.stream = stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = overlap ? 1 : 0;
+        const bool even = skinny_env().even_grid != 0;
+        const int variant = skinny_env().depth;  // experiment: which instantiation (0 = default)
         cudaError_t e;
-        if (kb_count <= 16)
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<1, 4, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias, p.scaled);
-        else if (kb_count <= 32)
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<2, 2, 2>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias, p.scaled);
-        else
-            e = cudaLaunchKernelEx(&cfg, gemm_s4_skinny_reg_kernel<4, 2, 1>, x, w, y, p.m, p.n, p.k, s.groups_total, overlap, p.bias, p.scaled);
+        if (kb_count <= 16) {
+            e = variant == 4 ? reg_launch<1, 4, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even)
+                             : reg_launch<1, 8, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+        } else if (kb_count <= 32) {
+            if (variant == 2) e = reg_launch<2, 2, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+            else if (variant == 3) e = reg_launch<2, 3, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+            else if (variant == 6) e = reg_launch<1, 6, 1, 32>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+            else e = reg_launch<1, 8, 1, 32>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+        } else {
+            e = variant == 3 ? reg_launch<2, 3, 1, 32>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even)
+                             : reg_launch<4, 2, 1, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+        }
         count_launch();
         if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
         return INT4L_OK;

@@ -2,8 +2,10 @@
 //   * the kernel template launched with the geometry test/benchmark.cu:46-72 derives from
 //     the header's constants (grid, block, kSmemSize, 96 KiB opt-in), and
 //   * linear_v21_launch called as test/test_correctness.cu:60 calls it,
-// both compared bit for bit with a plain CPU loop on seeded operands.
+// both compared bit for bit with a plain CPU loop on seeded operands; then the template kernel
+// at 4096 x 4096 x 4096, checked and timed the way the reference benchmark times it.
 // Prints "PASS" and exits 0 when everything matches.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
@@ -65,11 +67,78 @@ static int check(int m, int n, int k)
     return 0;
 }
 
+// The template kernel at a benchmark-sized shape: bit-equal to the launcher's result everywhere
+// (the launcher is checked against the oracle by the other tests), equal to a CPU loop on sampled
+// rows, and timed with the method of test/benchmark.cu:71-115 (warm-ups, an L2 flush before every
+// timed launch, CUDA events, median, TOPS = 2mnk / t).
+static int check_large_and_time(int m, int n, int k)
+{
+    const size_t xw = size_t(m) * k / 8, ww = size_t(n) * k / 8;
+    std::vector<unsigned> xp(xw), wp(ww);
+    unsigned long long s = 0x9E3779B97F4A7C15ull * (m + 3ull * n + 7ull * k);
+    auto next = [&]() { s ^= s << 13; s ^= s >> 7; s ^= s << 17; return unsigned(s >> 32); };
+    for (auto& v : xp) v = next();
+    for (auto& v : wp) v = next();
+    void *xd, *wd, *yd, *yd2, *flush;
+    const size_t flush_bytes = size_t(256) << 20;
+    if (cudaMalloc(&xd, xw * 4) != cudaSuccess || cudaMalloc(&wd, ww * 4) != cudaSuccess ||
+        cudaMalloc(&yd, size_t(m) * n * 4) != cudaSuccess || cudaMalloc(&yd2, size_t(m) * n * 4) != cudaSuccess ||
+        cudaMalloc(&flush, flush_bytes) != cudaSuccess) { std::printf("allocation failed\n"); return 1; }
+    cudaMemcpy(xd, xp.data(), xw * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(wd, wp.data(), ww * 4, cudaMemcpyHostToDevice);
+
+    using config = LinearConfig<8, 7, 7, 6, 6, 4>;
+    cudaFuncSetAttribute(linear_v21_kernel<config>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    constexpr int n_threads = config::kWarpsPerThreadblockM * config::kWarpsPerThreadblockN * (1 << LOG2_WARP_SIZE);
+    dim3 block(n_threads, 1);
+    dim3 grid((n + config::kThreadblockShapeN - 1) / config::kThreadblockShapeN,
+              (m + config::kThreadblockShapeM - 1) / config::kThreadblockShapeM);
+    LinearArgs args = {.X_ptr = xd, .W_ptr = wd, .Y_ptr = yd, .m = m, .n = n, .k = k};
+    cudaMemset(yd, 0xFF, size_t(m) * n * 4);
+    for (int i = 0; i < 5; ++i) linear_v21_kernel<config><<<grid, block, config::kSmemSize>>>(args);
+    if (linear_v21_kernel_status() != 0) { std::printf("template kernel reported a failure\n"); return 1; }
+    linear_v21_launch(xd, wd, yd2, m, n, k);
+    std::vector<int> a(size_t(m) * n), b(size_t(m) * n);
+    cudaMemcpy(a.data(), yd, a.size() * 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(b.data(), yd2, b.size() * 4, cudaMemcpyDeviceToHost);
+    size_t bad = 0;
+    for (size_t i = 0; i < a.size(); ++i) bad += a[i] != b[i];
+    if (bad) { std::printf("template kernel differs from the launcher in %zu places at %dx%dx%d\n", bad, m, n, k); return 1; }
+    auto nib = [](unsigned word, int t) { int v = (word >> (4 * t)) & 15; return v >= 8 ? v - 16 : v; };
+    for (int i = 0; i < m; i += m / 8 + 1)
+        for (int j = 0; j < n; ++j) {
+            int acc = 0;
+            for (int l = 0; l < k; ++l) acc += nib(xp[size_t(i) * (k / 8) + l / 8], l % 8) * nib(wp[size_t(j) * (k / 8) + l / 8], l % 8);
+            if (acc != a[size_t(i) * n + j]) { std::printf("template kernel wrong at (%d, %d)\n", i, j); return 1; }
+        }
+
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    const int iters = 21;
+    std::vector<float> ms(iters);
+    for (int i = 0; i < iters; ++i) {
+        cudaMemsetAsync(flush, i, flush_bytes);
+        cudaEventRecord(e0);
+        linear_v21_kernel<config><<<grid, block, config::kSmemSize>>>(args);
+        cudaEventRecord(e1);
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(&ms[i], e0, e1);
+    }
+    std::sort(ms.begin(), ms.end());
+    const double tops = 2.0 * m * n * double(k) / (ms[iters / 2] * 1e9);
+    std::printf("[PERF] template kernel %dx%dx%d: %.4f ms median, %.1f TOPS\n", m, n, k, ms[iters / 2], tops);
+    cudaFree(xd); cudaFree(wd); cudaFree(yd); cudaFree(yd2); cudaFree(flush);
+    return 0;
+}
+
 int main()
 {
-    const int shapes[][3] = {{256, 128, 128}, {300, 200, 96}, {64, 258, 512}, {513, 129, 1056}};
+    const int shapes[][3] = {{256, 128, 128}, {300, 200, 96}, {64, 258, 512}, {513, 129, 1056}, {1000, 520, 4096}, {256, 128, 32}};
     for (auto& s : shapes)
         if (check(s[0], s[1], s[2])) return 1;
+    if (linear_v21_kernel_status() != 0) { std::printf("template kernel reported a failure\n"); return 1; }
+    if (check_large_and_time(4096, 4096, 4096)) return 1;
     std::printf("PASS\n");
     return 0;
 }

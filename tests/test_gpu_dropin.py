@@ -1,7 +1,9 @@
 """GPU: the drop-in boundary.  (1) tests/compat_check.cu uses the replacement header exactly as
 the reference's harnesses do (kernel template with the harness-derived launch geometry, and
 linear_v21_launch) and compares with a CPU loop.  (2) Where it was built, the reference's own
-test/test_correctness.cu -- unchanged, linked against this library -- must run to completion."""
+test/test_correctness.cu -- unchanged, linked against this library -- must run to completion; that
+program's own comparison is commented out upstream (test/test_correctness.cu:66-76), so this shows
+that it links and runs, nothing more: the results of that boundary are checked by (1)."""
 import os
 import subprocess
 
@@ -18,6 +20,12 @@ def test_compat_header_and_launcher(cuda):
     r = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "PASS" in r.stdout
+    # The template kernel is a tensor-memory kernel, not a compatibility stub: a loose floor on its
+    # rate at 4096^3 (it measures around fifteen times this on an idle B200).
+    perf = [line for line in r.stdout.splitlines() if line.startswith("[PERF]")]
+    assert perf, r.stdout
+    print(perf[0])
+    assert float(perf[0].split()[-2]) > 100.0, perf[0]
 
 
 def test_reference_correctness_program_runs_unchanged(cuda):
@@ -62,10 +70,9 @@ def test_reference_gpu_kernel_agrees(cuda):
     assert O.is_same(y_ours.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("version", [0, 1, 2, 10, 11, 20, 21])
-def test_launcher_of_every_reference_generation(cuda, version):
-    """Every linear_vN_launch symbol (C++ linkage, as the reference declares them) computes the
-    operator: called through its mangled name with device pointers."""
+def test_reference_launcher_symbol_computes_the_operator(cuda, version=21):
+    """linear_v21_launch with C++ linkage, as the reference declares it (kernels/linear_v21.h:760):
+    called through its mangled name with device pointers."""
     import ctypes
     import numpy as np
     import torch
