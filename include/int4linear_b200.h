@@ -79,6 +79,24 @@ int int4_linear_bias_launch_async(const void* x_packed_d, const void* w_packed_d
                                   void* y_d, int m, int n, int k, void* stream);
 
 /*
+ * The operator for a stream of small-batch (decode) launches, with per-call promises instead of
+ * the process-wide switch of int4_linear_set_overlap.  `promises` is a bit set:
+ *   INT4L_PROMISE_WEIGHTS_STATIONARY  w_packed_d is not written by anything queued before this
+ *                                     launch in `stream` (a linear layer's weights never are);
+ *   INT4L_PROMISE_X_NOT_PENDING       the same for x_packed_d (valid only together with the first).
+ * With a promise the launch may begin while its predecessor in the stream is still running
+ * (programmatic dependent launch) and stream the promised operands early; everything it was not
+ * promised is read, and Y is written, only after the predecessor has completed.  For shapes that
+ * the decode kernels do not serve (m > 32) the promises are ignored.  0 = an ordinary launch.
+ * bias_d as in int4_linear_bias_launch_async.  No reference counterpart: the reference launcher
+ * synchronises the device after every call (kernels/linear_v21.cu:39).
+ */
+#define INT4L_PROMISE_WEIGHTS_STATIONARY 1
+#define INT4L_PROMISE_X_NOT_PENDING      2
+int int4_linear_decode_launch_async(const void* x_packed_d, const void* w_packed_d, const int* bias_d, void* y_d,
+                                    int m, int n, int k, int promises, void* stream);
+
+/*
  * The operator with a dequantising epilogue and bfloat16 output:
  *     Y16[i][j] = bf16( float(sum_l X[i][l] * W[j][l]) * row_scale[i] * col_scale[j] + bias[j] )
  * row_scale_d (m floats, per-token), col_scale_d (n floats, per-channel) and bias_d (n floats)

@@ -15,6 +15,7 @@ from .linear import (  # noqa: F401
     linear,
     linear_host,
     linear_prepared,
+    linear_decode,
     linear_expanded,
     linear_scaled,
     prepare_weights,

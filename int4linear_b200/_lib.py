@@ -13,6 +13,7 @@ SYMBOLS = {
     "int4_linear_launch": (None, [_VP, _VP, _VP, _I, _I, _I]),
     "int4_linear_launch_async": (_I, [_VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_bias_launch_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
+    "int4_linear_decode_launch_async": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
     "int4_linear_scaled_launch_async": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_scaled_f16_launch_async": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP]),
     "int4_linear_launch_gather_async": (_I, [_VP, _VP, _VP, ctypes.POINTER(ctypes.c_void_p), _I, _I, _I, _I, _I, _I, _VP]),

@@ -429,6 +429,22 @@ int int4_linear_bias_launch_async(const void* x, const void* w, const int* bias_
     return rc;
 }
 
+int int4_linear_decode_launch_async(const void* x, const void* w, const int* bias_d, void* y, int m, int n, int k,
+                                    int promises, void* stream)
+{
+    int rc = check_args(x, w, y, m, n, k);
+    if (rc == INT4L_OK && bias_d != nullptr && (reinterpret_cast<uintptr_t>(bias_d) & 3u)) rc = INT4L_ERR_MISALIGNED;
+    if (rc == INT4L_OK && (promises < 0 || promises > 3 || promises == INT4L_PROMISE_X_NOT_PENDING)) rc = INT4L_ERR_INVALID_ARG;
+    if (rc != INT4L_OK) { t_last_status = rc; return rc; }
+    DeviceCtx* ctx = current_ctx(&rc);
+    if (!ctx) { t_last_status = rc; return rc; }
+    Problem p{x, w, y, m, n, k, bias_d};
+    p.overlap = promises == 0 ? 0 : (promises == INT4L_PROMISE_WEIGHTS_STATIONARY ? 1 : 2);
+    rc = dispatch(ctx, p, static_cast<cudaStream_t>(stream));
+    t_last_status = rc;
+    return rc;
+}
+
 int int4_linear_prepare_weights(const void* w_packed_d, void* w_expanded_d, int n, int k, void* stream)
 {
     int rc = check_args(w_packed_d, w_packed_d, w_expanded_d, 1, n, k);

@@ -49,6 +49,9 @@ struct Problem {
     // int4_linear_prepare_weights (N x K bytes).
     bool w_expanded = false;
     ScaledOut scaled;
+    // Launch-overlap promise of this call (int4_linear_decode_launch_async): -1 = the process-wide
+    // setting of int4_linear_set_overlap, else 0, 1 or 2 with the same meaning.
+    int overlap = -1;
 };
 
 // One remembered tensor map: encoding costs a driver call of a microsecond or two, and a

@@ -89,6 +89,33 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
     }
 }
 
+// Clears 32 rows x `width` columns of Y (the rows of one epilogue warp) ahead of partial sums that
+// will be added into them, and returns only when the zeros have been performed in memory.
+template <bool kTmaStore>
+__device__ __forceinline__ void clear_rows(int width, int row0, int col0, int m, int n, int* __restrict__ y,
+                                           const CUtensorMap* tm_y, int col_shift, uint32_t stage0, int lane)
+{
+    if constexpr (kTmaStore) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) sts128(stage0 + lane * 128 + (q << 4), make_uint4(0u, 0u, 0u, 0u));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            for (int c = 0; c < width; c += 32)
+                if (row0 < m && col0 + c < n) tma_store_2d(tm_y, stage0, col_shift + col0 + c, row0);
+            tma_store_commit();
+            tma_store_wait_all<0>();  // performed, not merely read from the staging buffer
+        }
+        __syncwarp();
+    } else {
+        const int row = row0 + lane;
+        if (row < m)
+            for (int c = 0; c < width && col0 + c < n; ++c) y[static_cast<size_t>(row) * n + col0 + c] = 0;
+        __threadfence();
+        __syncwarp();
+    }
+}
+
 // Dequantising variant: float(acc) * row_scale[row] * col_scale[col] + bias[col], rounded to
 // bfloat16 or half (round to nearest even), written with per-thread 16-byte stores (8 values) where the
 // row pitch allows.  The int32 -> float conversion is exact (|acc| <= 64 K < 2^24).

@@ -286,7 +286,7 @@ gemm_s4_skinny_reg_kernel(const uint8_t* __restrict__ x, const uint8_t* __restri
 }
 
 
-// TMA variant for m <= 16: the decode shape proper.
+// Tensor-map variant for m <= 16 and K outside the range of the register variant.
 // Every warp owns K slices of 128 packed bytes (256 elements).  For a slice it asks TMA
 // for a box of [R rows x 128 B] of W -- all rows of the CTA's run at once when they fit,
 // so that the whole weight slab of the CTA is requested in the first microsecond of the
@@ -422,10 +422,10 @@ gemm_s4_skinny_tma_kernel(const __grid_constant__ CUtensorMap tm_w, const uint8_
 // launch lasts microseconds; a getenv per launch would show):
 //   INT4L_SKINNY_CTAS_PER_SM = 1 | 2   CTAs per SM of the register variant
 //   INT4L_SKINNY_ROWS / INT4L_SKINNY_BUFS   stage geometry of the TMA variant
-//   INT4L_SKINNY_DEPTH   groups of weight loads in flight per warp of the register variant
-//   INT4L_SKINNY_EVEN_GRID = 0   grid = all CTA slots instead of equal shares per CTA
+//   INT4L_SKINNY_DEPTH = 8   eight instead of four groups of weight loads in flight per warp (K <= 2048)
+//   INT4L_SKINNY_EVEN_GRID = 1   equal shares of 8-row groups per CTA instead of a CTA in every slot
 struct SkinnyEnv {
-    int ctas_per_sm = 0, stage_rows = 0, n_buffers = 2, depth = 0, even_grid = 1;
+    int ctas_per_sm = 0, stage_rows = 0, n_buffers = 2, depth = 0, even_grid = 0;
 };
 const SkinnyEnv& skinny_env()
 {
@@ -522,10 +522,6 @@ int setup_skinny(DeviceCtx*)
     if (e == cudaSuccess) e = reg_attr<1, 4, 2, 16>();
     if (e == cudaSuccess) e = reg_attr<1, 8, 2, 16>();
     if (e == cudaSuccess) e = reg_attr<2, 2, 2, 16>();
-    if (e == cudaSuccess) e = reg_attr<2, 3, 2, 16>();
-    if (e == cudaSuccess) e = reg_attr<1, 8, 1, 32>();
-    if (e == cudaSuccess) e = reg_attr<1, 6, 1, 32>();
-    if (e == cudaSuccess) e = reg_attr<2, 3, 1, 32>();
     if (e == cudaSuccess) e = reg_attr<4, 2, 1, 16>();
     return e == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }
@@ -541,7 +537,7 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     if (p.m <= 16 && kb_count >= 16 && kb_count <= 64 && skinny_variant() != 2 && skinny_variant() != 3) {
         // Two CTAs per SM: consecutive launches (overlap modes) can then be resident together,
         // so one launch streams weights while the previous one merges and writes its result.
-        const int overlap = stream_overlap_mode();
+        const int overlap = p.overlap >= 0 ? p.overlap : stream_overlap_mode();
         // One CTA per SM when launches may fully overlap (two launches then share each SM);
         // otherwise two, which hides more latency inside a single launch.
         int ctas_per_sm = overlap == 2 ? 1 : 2;
@@ -554,19 +550,15 @@ int launch_skinny(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
         cfg.attrs = attr;
         cfg.numAttrs = overlap ? 1 : 0;
         const bool even = skinny_env().even_grid != 0;
-        const int variant = skinny_env().depth;  // experiment: which instantiation (0 = default)
+        const int variant = skinny_env().depth;  // experiment: 8 = eight instead of four groups in flight (K <= 2048)
         cudaError_t e;
         if (kb_count <= 16) {
-            e = variant == 4 ? reg_launch<1, 4, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even)
-                             : reg_launch<1, 8, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+            e = variant == 8 ? reg_launch<1, 8, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even)
+                             : reg_launch<1, 4, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
         } else if (kb_count <= 32) {
-            if (variant == 2) e = reg_launch<2, 2, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
-            else if (variant == 3) e = reg_launch<2, 3, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
-            else if (variant == 6) e = reg_launch<1, 6, 1, 32>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
-            else e = reg_launch<1, 8, 1, 32>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+            e = reg_launch<2, 2, 2, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
         } else {
-            e = variant == 3 ? reg_launch<2, 3, 1, 32>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even)
-                             : reg_launch<4, 2, 1, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
+            e = reg_launch<4, 2, 1, 16>(cfg, ctas_per_sm, ctx, p, s.groups_total, overlap, even);
         }
         count_launch();
         if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }

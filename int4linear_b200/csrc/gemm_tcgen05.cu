@@ -260,6 +260,21 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         uint32_t chunk_no = 0;
         bool alive = true;
         Segment sg;
+        // Tiles that are cut along K receive nothing but additions, so somebody has to clear them
+        // first: the worker whose share holds K block 0 of such a tile does it here, while the
+        // pipeline is still filling, and raises the tile's flag; by the time any share of the tile
+        // is finished the flag has long been up, and no share waits for another's epilogue.
+        for (int si = 0; segment_of(sched, worker, BN, si, &sg); ++si) {
+            if (sg.mode != kSegOwner) continue;
+            int tm, tn;
+            tile_coord(sg.tile, tm, tn);
+            const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
+            unsigned* flag = sched.flags + ((static_cast<size_t>(sg.sk_index) * CTAS + cta_rank) * 4 + sp) * 2;
+            clear_rows<kTmaStore>(sg.width, row0, tn * BN + sg.col_off, m, n, y, y_maps, col_shift, stage0, lane);
+            if (lane == 0) flag_raise(flag);
+            __syncwarp();
+            break;  // a worker's share contains the start of at most one tile
+        }
         for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si, ++local_tile) {
             int tm, tn;
             tile_coord(sg.tile, tm, tn);
@@ -270,8 +285,8 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
-            // Flag pair of these 32 rows of a tile that is cut along K: [0] raised by the owner once
-            // its stores have landed, [1] counts the adders that have seen it.
+            // Flag pair of these 32 rows of a tile that is cut along K: [0] raised once the rows have
+            // been cleared, [1] counts the shares that have seen it.
             unsigned* flag = sched.flags + ((static_cast<size_t>(sg.sk_index) * CTAS + cta_rank) * 4 + sp) * 2;
             if (so.y16 != nullptr) {
                 // Dequantised bf16 output; y_maps[0] then describes the bf16 matrix.
@@ -280,24 +295,20 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                     else drain_accumulator_scaled_tma<false>(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
                 }
                 else drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
-            } else if (sg.mode == kSegAdd) {
-                // Partial sums of a tile another worker owns: wait until its stores are in place.
+            } else if (sg.mode != kSegStore) {
+                // A share of a tile that is cut along K: added into Y once the tile has been cleared
+                // (long ago, see above); the share that holds K block 0 brings the bias.
+                if (sg.sk_index < 0 || sg.sk_index >= kSkMaxTiles || sched.flags == nullptr) { *abort_flag = 1; alive = false; break; }
                 if (!flag_wait(flag, abort_flag, lane)) { alive = false; break; }
-                drain_accumulator<kTmaStore, true>(t_addr, width, row0, col0, m, n, y, nullptr, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
-                if (lane == 0 && atomicAdd(flag + 1, 1u) == static_cast<unsigned>(sg.adders - 1)) {
-                    // Every adder of these rows has passed its wait: leave the pair clean for the next launch.
+                drain_accumulator<kTmaStore, true>(t_addr, width, row0, col0, m, n, y, sg.mode == kSegOwner ? bias : nullptr,
+                                                   y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
+                if (lane == 0 && atomicAdd(flag + 1, 1u) == static_cast<unsigned>(sg.adders)) {
+                    // Every share of these rows has passed its wait: leave the pair clean for the next launch.
                     flag[0] = 0;
                     flag[1] = 0;
                 }
             } else {
                 drain_accumulator<kTmaStore, false>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
-                if (sg.mode == kSegOwner) {
-                    if (lane == 0) {
-                        if constexpr (kTmaStore) tma_store_wait_all<0>();  // the stores have been performed, not just read
-                        flag_raise(flag);
-                    }
-                    __syncwarp();
-                }
             }
             tc_fence_before_sync();
             __syncwarp();

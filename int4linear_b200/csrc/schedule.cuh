@@ -9,18 +9,18 @@
 //                 sk_tiles * kb_count K blocks -- and that line is cut into `sk_workers`
 //                 contiguous, near-equal ranges, one per worker.  A range covers the end of one
 //                 tile and/or the start of the next, so a worker computes at most two partial
-//                 tiles ("segments").  The segment that contains K block 0 of a tile OWNS the
-//                 tile: it stores its partial sums (plus bias) with ordinary stores and then
-//                 raises a flag; the other segments of the tile wait for that flag and ADD their
-//                 partial sums into Y (integer adds commute, so the result is bit-exact and
-//                 does not depend on arrival order);
+//                 tiles ("segments").  Every segment ADDS its partial sums into Y (integer adds
+//                 commute, so the result is bit-exact and does not depend on arrival order).  The
+//                 worker whose range contains K block 0 of a tile OWNS it: at the very start of
+//                 the kernel it clears the tile in Y and raises the tile's flag, its segment also
+//                 brings the bias; every segment checks the flag before it adds;
 //   half tiles    where partial sums cannot be added into the output (rounded 16-bit output, a
 //                 result that is stored into several GPUs), a last wave that fills at most half
 //                 of the workers is cut into half-width items instead.
 //
-// A worker runs its whole tiles first, then the segment it owns, then the segment it adds, so an
-// adding segment always comes last and the flag it needs was raised long before: waiting
-// segments never hold up anything another worker waits for.
+// A worker runs its whole tiles first, then the segment of the tile it owns, then the other one.
+// The flags are raised in the first microsecond of the kernel by epilogue warps that have nothing
+// else to do yet, so no segment ever waits for another segment's work.
 #pragma once
 
 #include <stdint.h>
@@ -56,7 +56,7 @@ struct Segment {
     int col_off, width;  // columns of the tile this item covers (half-width items)
     int mode;            // SegMode
     int sk_index;        // tile - whole, for the flag slot (stream-K segments)
-    int adders;          // segments that add into this tile (stream-K)
+    int adders;          // segments of this tile besides the owner's (stream-K)
 };
 
 // First K block (in the stream-K line) of worker w.

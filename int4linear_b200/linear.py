@@ -137,6 +137,33 @@ def linear(x_packed, w_packed, k: int | None = None, out=None, stream=None, bias
     return out
 
 
+def linear_decode(x_packed, w_packed, out=None, bias=None, weights_stationary=True, x_not_pending=False, stream=None):
+    """Y = X @ W^T (+ bias) for a stream of small-batch launches (int4_linear_decode_launch_async):
+    `weights_stationary` promises that nothing queued before this launch writes W, `x_not_pending`
+    the same for X; with a promise consecutive launches overlap on the GPU."""
+    import torch
+    xb = x_packed.contiguous().view(torch.uint8)
+    wb = w_packed.contiguous().view(torch.uint8)
+    m, n, k = xb.shape[0], wb.shape[0], xb.shape[1] * 2
+    if wb.shape[1] * 2 != k:
+        raise ValueError("packed widths do not match")
+    if x_not_pending and not weights_stationary:
+        raise ValueError("x_not_pending is valid only together with weights_stationary")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.int32, device=xb.device)
+    elif tuple(out.shape) != (m, n) or out.dtype != torch.int32 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous int32 tensor of shape [m, n]")
+    promises = (1 if weights_stationary else 0) | (2 if x_not_pending else 0)
+    handle = (stream or torch.cuda.current_stream(xb.device)).cuda_stream
+    with torch.cuda.device(xb.device):
+        st = _lib.load().int4_linear_decode_launch_async(
+            xb.data_ptr(), wb.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            m, n, k, promises, handle)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_decode_launch_async")
+    return out
+
+
 def linear_scaled(x_packed, w_packed, row_scale=None, col_scale=None, bias=None, out=None, stream=None, dtype=None):
     """16-bit Y = (X @ W^T) * row_scale[:, None] * col_scale[None, :] + bias (see
     int4_linear_scaled_launch_async).  Scales and bias are CUDA float32 vectors or None; `dtype` is

@@ -433,3 +433,58 @@ def test_empty_shard_returns_an_empty_result(cuda):
     y = L.linear(xd, wd)
     assert tuple(y.shape) == (64, 0) and y.dtype == torch.int32
     assert L.launch_count() == before
+
+
+@pytest.mark.parametrize("promises", [(False, False), (True, False), (True, True)], ids=["none", "weights", "weights+x"])
+def test_decode_launches_with_per_call_promises(cuda, promises):
+    """int4_linear_decode_launch_async: the launch-overlap promise given per call instead of through
+    the process-wide switch.  A chain of launches over distinct weights into one Y buffer, a
+    snapshot after each: every result exact, with a bias, and X produced on the same stream just
+    before the first launch when X is not promised."""
+    import torch
+    weights_stationary, x_not_pending = promises
+    m, n, k = 12, 3080, 4096
+    x = L.uniform_s4(51, m, k)
+    ws = [L.uniform_s4(60 + i, n, k) for i in range(3)]
+    wds = [torch.from_numpy(L.pack_bytes(w)).to(cuda) for w in ws]
+    bias = torch.from_numpy(((np.arange(n) * 13) % 801 - 400).astype(np.int32)).to(cuda)
+    x_src = torch.from_numpy(L.pack_bytes(x)).to(cuda)
+    xd = torch.zeros_like(x_src)
+    yd = torch.empty((m, n), dtype=torch.int32, device=cuda)
+    if x_not_pending:
+        xd.copy_(x_src)
+        torch.cuda.synchronize()
+    outs = []
+    for rep in range(3):
+        if not x_not_pending:
+            xd.copy_(x_src)  # X is written by work queued right in front of the launch
+        for wd in wds:
+            L.linear_decode(xd, wd, out=yd, bias=bias, weights_stationary=weights_stationary, x_not_pending=x_not_pending)
+            outs.append(yd.clone())
+    torch.cuda.synchronize()
+    assert L.last_status() == 0
+    refs = [O.linear_ref_sgemm(x, w) + bias.cpu().numpy()[None, :] for w in ws]
+    for i, out in enumerate(outs):
+        assert O.is_same(out.cpu().numpy(), refs[i % 3]), f"launch {i}"
+    lib = _lib_for_args()
+    p = xd.data_ptr()
+    assert lib.int4_linear_decode_launch_async(p, p, None, p, 8, 8, 32, 2, None) == 1   # X promised without W
+    assert lib.int4_linear_decode_launch_async(p, p, None, p, 8, 8, 32, 4, None) == 1
+
+
+def _lib_for_args():
+    from int4linear_b200 import _lib
+    return _lib.load()
+
+
+@pytest.mark.parametrize("m", [33, 64, 96, 128])
+@pytest.mark.parametrize("n,k", [(264, 1024), (264, 4096), (14336, 1024), (14336, 4096)])
+def test_a_few_dozen_rows(cuda, m, n, k):
+    """33 <= M <= 128 (a batch of decode requests, a short prefill): one row block of tiles whose
+    K range the schedule cuts across the SMs.  Automatic dispatch and the forced tile widths."""
+    x, w, xp, wp = make_case(m, n, k, seed=17)
+    ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+    assert L.path_for(m, n, k) == L.PATH_TCGEN05
+    assert O.is_same(run_device(cuda, xp, wp, k), ref)
+    for tile_n in (128, 256):
+        assert O.is_same(run_device(cuda, xp, wp, k, path=L.PATH_TCGEN05, tile_n=tile_n), ref), f"tile_n={tile_n}"
