@@ -416,7 +416,7 @@ def main():
     ap.add_argument("--variant", default="default", choices=["default", "two-pass", "prepared"],
                     help="opt-in variants of the tensor-memory path: expand pre-pass + byte GEMM, weights "
                          "pre-expanded outside the timed region")
-    ap.add_argument("--tail", default="auto", choices=["auto", "none", "half", "streamk"],
+    ap.add_argument("--tail", default="auto", choices=["auto", "none", "half"],
                     help="how a last, partial wave of tiles is run (int4_linear_set_tail)")
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
@@ -480,7 +480,7 @@ def main():
     numa_info = numa.bind_to_gpu_node(bus) if bus else {"node": None, "cpus": 0, "bound": False}
     L.set_path({"auto": L.PATH_AUTO, "tcgen05": L.PATH_TCGEN05, "legacy": L.PATH_LEGACY,
                 "skinny": L.PATH_SKINNY}[args.path])
-    L.set_tail({"auto": -1, "none": 0, "half": 1, "streamk": 2}[args.tail])
+    L.set_tail({"auto": -1, "none": 0, "half": 1}[args.tail])
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 

@@ -251,13 +251,10 @@ int int4_linear_set_path(int path);
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
 
 /* How the tensor-memory kernels run a last wave of output tiles that does not fill the GPU:
- * -1 (default) automatic; 0 as whole tiles; 1 as half-width items when at most half of the CTA
- * pairs would be busy; 2 cut along K into equal shares for all workers, the partial sums of a
- * tile being added into Y by bulk reductions after the share that holds the start of K has stored
- * its part (integer addition: the result is bit-identical whatever the order).  Mode 2 applies to
- * int32 output on one GPU only; the automatic choice uses it where it saves time, else mode 1.
- * Replaces the fixed one-CTA-per-tile grid of kernels/linear_v21.cu:20-37.
- * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_TAIL=none|half|streamk. */
+ * -1 (default) and 1: as half-width items when at most half of the CTA pairs would be busy
+ * (about three quarters of a tile time instead of a whole one); 0: as whole tiles.  The results
+ * are identical.  Replaces the fixed one-CTA-per-tile grid of kernels/linear_v21.cu:20-37.
+ * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_TAIL=none|half. */
 int int4_linear_set_tail(int mode);
 
 /* Overlap of back-to-back decode-shape launches in one stream (programmatic dependent

@@ -136,7 +136,6 @@ int tail_mode()
         v = -1;
         if (e && !std::strcmp(e, "none")) v = 0;
         else if (e && !std::strcmp(e, "half")) v = 1;
-        else if (e && !std::strcmp(e, "streamk")) v = 2;
         g_tail.store(v);
     }
     return v;
@@ -287,11 +286,7 @@ int poll_device_status(DeviceCtx* ctx)
 {
     if (!ctx || !ctx->status_host) return INT4L_OK;
     int s = *ctx->status_host;
-    if (s != INT4L_OK) {
-        *ctx->status_host = INT4L_OK;
-        // A kernel that gave up may have left hand-over flags raised; the next launch needs them clear.
-        if (ctx->sk_flags != nullptr && cudaMemset(ctx->sk_flags, 0, ctx->sk_flag_bytes) != cudaSuccess) cudaGetLastError();
-    }
+    if (s != INT4L_OK) *ctx->status_host = INT4L_OK;
     return s;
 }
 
@@ -693,7 +688,7 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
 
 int int4_linear_set_tail(int mode)
 {
-    if (mode < -1 || mode > 2) return INT4L_ERR_INVALID_ARG;
+    if (mode < -1 || mode > 1) return INT4L_ERR_INVALID_ARG;
     g_tail.store(mode);
     return INT4L_OK;
 }

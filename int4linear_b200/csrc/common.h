@@ -7,7 +7,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include <atomic>
 #include <mutex>
 
 #include "../../include/int4linear_b200.h"
@@ -92,10 +91,6 @@ struct DeviceCtx {
     size_t stage_w_src_bytes = 0;
     // Scratch of the two-pass path (expanded operands), grown on demand.
     void* scratch = nullptr; size_t scratch_bytes = 0;
-    // Hand-over flags of the tiles the tensor-memory kernel cuts along K, and how many launches
-    // have taken a set of them.
-    unsigned* sk_flags = nullptr; size_t sk_flag_bytes = 0;
-    std::atomic<unsigned long long> sk_launches{0};
     bool attrs_set = false;
 };
 
@@ -157,7 +152,7 @@ bool getenv_flag_direct_store();
 int forced_tile_n();
 int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
 int two_pass_mode();  // -1 automatic, 0 never, 1 whenever the tensor-memory family is used
-int tail_mode();  // int4_linear_set_tail: -1 automatic, 0 whole tiles only, 1 half-width items, 2 cut along K
+int tail_mode();  // int4_linear_set_tail: -1 automatic, 0 whole tiles only, 1 half-width items
 int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always (m > 128)
 
 }  // namespace i4l

@@ -19,9 +19,7 @@
 
 namespace i4l {
 
-// kAdd: the values are partial sums of a tile that is cut along K and are added into Y (bulk
-// reduction, or atomic adds on the per-thread path) instead of stored.
-template <bool kTmaStore, bool kAdd = false>
+template <bool kTmaStore>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, int row0, int col0, int m, int n,
                                                   int* __restrict__ y, const int* __restrict__ bias,
                                                   const CUtensorMap* tm_y, int n_maps, int col_shift,
@@ -59,9 +57,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
             if (lane == 0) {
                 // One store per destination matrix (one normally; every rank's copy of the full Y
                 // when the result is gathered through peer memory), all from the same staging tile.
-                if constexpr (kAdd) tma_reduce_add_2d(tm_y, stg, col_shift + col0 + c, row0);
-                else
-                    for (int d = 0; d < n_maps; ++d) tma_store_2d(tm_y + d, stg, col_shift + col0 + c, row0);
+                for (int d = 0; d < n_maps; ++d) tma_store_2d(tm_y + d, stg, col_shift + col0 + c, row0);
                 tma_store_commit();
             }
             ++chunk_no;
@@ -71,11 +67,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int col = col0 + c + 4 * q;
-                    if constexpr (kAdd) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (col + e < n) atomicAdd(dst + 4 * q + e, static_cast<int>(v[4 * q + e]));
-                    } else if (vec_ok && col + 3 < n) {
+                    if (vec_ok && col + 3 < n) {
                         *reinterpret_cast<int4*>(dst + 4 * q) =
                             make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     } else {
@@ -86,33 +78,6 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
                 }
             }
         }
-    }
-}
-
-// Clears 32 rows x `width` columns of Y (the rows of one epilogue warp) ahead of partial sums that
-// will be added into them, and returns only when the zeros have been performed in memory.
-template <bool kTmaStore>
-__device__ __forceinline__ void clear_rows(int width, int row0, int col0, int m, int n, int* __restrict__ y,
-                                           const CUtensorMap* tm_y, int col_shift, uint32_t stage0, int lane)
-{
-    if constexpr (kTmaStore) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) sts128(stage0 + lane * 128 + (q << 4), make_uint4(0u, 0u, 0u, 0u));
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-            for (int c = 0; c < width; c += 32)
-                if (row0 < m && col0 + c < n) tma_store_2d(tm_y, stage0, col_shift + col0 + c, row0);
-            tma_store_commit();
-            tma_store_wait_all<0>();  // performed, not merely read from the staging buffer
-        }
-        __syncwarp();
-    } else {
-        const int row = row0 + lane;
-        if (row < m)
-            for (int c = 0; c < width && col0 + c < n; ++c) y[static_cast<size_t>(row) * n + col0 + c] = 0;
-        __threadfence();
-        __syncwarp();
     }
 }
 

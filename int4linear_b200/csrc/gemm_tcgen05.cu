@@ -84,8 +84,6 @@ struct Cfg {
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-constexpr size_t kSkFlagWordsPerRegion = static_cast<size_t>(kSkMaxTiles) * 2 /*CTAs*/ * 4 /*warps*/ * 2 /*words*/;
-
 // Destination tensor maps of the gathering variant: the full Y of every rank of the node.
 constexpr int kMaxPeers = 8;
 struct PeerMaps {
@@ -173,9 +171,9 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         if constexpr (CTAS == 2) cluster_wait();
     }
 
-    // Every role walks the same list of segments (schedule.cuh): whole tiles, half-width items,
-    // K ranges of the tiles that are cut along K.
+    // Every role walks the same list of items (schedule.cuh): whole tiles, then half-width items.
     const int tiles_m = sched.tiles_m, tiles_n = sched.tiles_n;
+    const int kb_count = (k + 127) / 128;
     constexpr int kGroupM = 16;  // tiles of 16 consecutive M blocks share their W panel in L2
     auto tile_coord = [&](int tile, int& tm, int& tn) {
         const int group_size = kGroupM * tiles_n;
@@ -197,7 +195,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 int tm, tn;
                 tile_coord(sg.tile, tm, tn);
                 const int rows_w = sg.width / CTAS;
-                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const uint32_t s = it % P, r = it / P;
                     if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                     mbar_expect_tx(pk_full(s), C::kPreW ? C::kPkStage : (kBM + rows_w) * kBKBytes);
@@ -232,7 +230,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 if (!mbar_wait(tm_empty(buf), (br & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                for (int kb = 0; kb < kb_count; ++kb, ++it) {
                     const uint32_t s = it % U, r = it / U;
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
                     tc_fence_after_sync();
@@ -242,7 +240,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // 32 bytes of K per instruction: advance the start address field by 32 >> 4.
-                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb != sg.kb0 || j != 0) ? 1u : 0u);
+                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
                     if constexpr (CTAS == 2) umma_commit_2cta(up_empty(s), 3); else umma_commit(up_empty(s));
                 }
@@ -260,21 +258,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         uint32_t chunk_no = 0;
         bool alive = true;
         Segment sg;
-        // Tiles that are cut along K receive nothing but additions, so somebody has to clear them
-        // first: the worker whose share holds K block 0 of such a tile does it here, while the
-        // pipeline is still filling, and raises the tile's flag; by the time any share of the tile
-        // is finished the flag has long been up, and no share waits for another's epilogue.
-        for (int si = 0; segment_of(sched, worker, BN, si, &sg); ++si) {
-            if (sg.mode != kSegOwner) continue;
-            int tm, tn;
-            tile_coord(sg.tile, tm, tn);
-            const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
-            unsigned* flag = sched.flags + ((static_cast<size_t>(sg.sk_index) * CTAS + cta_rank) * 4 + sp) * 2;
-            clear_rows<kTmaStore>(sg.width, row0, tn * BN + sg.col_off, m, n, y, y_maps, col_shift, stage0, lane);
-            if (lane == 0) flag_raise(flag);
-            __syncwarp();
-            break;  // a worker's share contains the start of at most one tile
-        }
         for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si, ++local_tile) {
             int tm, tn;
             tile_coord(sg.tile, tm, tn);
@@ -285,9 +268,6 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * BN;
-            // Flag pair of these 32 rows of a tile that is cut along K: [0] raised once the rows have
-            // been cleared, [1] counts the shares that have seen it.
-            unsigned* flag = sched.flags + ((static_cast<size_t>(sg.sk_index) * CTAS + cta_rank) * 4 + sp) * 2;
             if (so.y16 != nullptr) {
                 // Dequantised bf16 output; y_maps[0] then describes the bf16 matrix.
                 if constexpr (kTmaStore) {
@@ -295,20 +275,8 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                     else drain_accumulator_scaled_tma<false>(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
                 }
                 else drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
-            } else if (sg.mode != kSegStore) {
-                // A share of a tile that is cut along K: added into Y once the tile has been cleared
-                // (long ago, see above); the share that holds K block 0 brings the bias.
-                if (sg.sk_index < 0 || sg.sk_index >= kSkMaxTiles || sched.flags == nullptr) { *abort_flag = 1; alive = false; break; }
-                if (!flag_wait(flag, abort_flag, lane)) { alive = false; break; }
-                drain_accumulator<kTmaStore, true>(t_addr, width, row0, col0, m, n, y, sg.mode == kSegOwner ? bias : nullptr,
-                                                   y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
-                if (lane == 0 && atomicAdd(flag + 1, 1u) == static_cast<unsigned>(sg.adders)) {
-                    // Every share of these rows has passed its wait: leave the pair clean for the next launch.
-                    flag[0] = 0;
-                    flag[1] = 0;
-                }
             } else {
-                drain_accumulator<kTmaStore, false>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
+                drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -340,7 +308,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si) {
             // 16-byte chunks to convert in this item's stages (a half-width item has fewer W rows)
             const int chunks = C::kPreW ? kChunks : (sg.width == BN ? kChunks : (kBM + C::kRowsW / 2) * 4);
-            for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+            for (int kb = 0; kb < kb_count; ++kb, ++it) {
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
@@ -461,23 +429,15 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     } else {
         tm_y = tm_x;  // unused by the kernel
     }
-    // The last, partial wave of tiles: cut along K where partial sums can be added into Y (int32
-    // output on this GPU), else as half-width items, else left as whole tiles (schedule.cuh).
+    // A last wave of tiles that would keep at most half of the CTA pairs busy is issued as
+    // half-width items (schedule.cuh).
     const int max_workers = C::kCtas == 2 ? ctx->max_pairs : ctx->sm_count;
-    const int tail = tail_mode();
-    const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr && gather == nullptr && ctx->sk_flags != nullptr;
-    const bool can_halve = (tail < 0 || tail == 1) && !C::kPreW && C::kCtas == 2;
-    Schedule sched = plan_schedule(tiles_m, tiles_n, (p.k + 127) / 128, max_workers, can_add, can_halve);
+    const bool can_halve = tail_mode() != 0 && !C::kPreW && C::kCtas == 2;
+    const Schedule sched = plan_schedule(tiles_m, tiles_n, max_workers, can_halve);
     tm_wh = tm_x;  // unused unless tiles are halved
     if (sched.half_tiles > 0) {
         rc = make_tensor_map_2d(ctx, &tm_wh, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW / 2, false);
         if (rc != INT4L_OK) return rc;
-    }
-    if (sched.sk_tiles > 0) {
-        // Launches take the flag sets in turn, so launches that overlap in time (different
-        // streams) do not share one unless kSkRegions of them are in flight at once.
-        const unsigned long long turn = ctx->sk_launches.fetch_add(1);
-        sched.flags = ctx->sk_flags + (turn % kSkRegions) * kSkFlagWordsPerRegion;
     }
     const int workers = sched.workers;
     cudaLaunchConfig_t cfg = {};
@@ -561,15 +521,6 @@ int setup_tcgen05(DeviceCtx* ctx)
         pairs = ctx->sm_count / 2;
     }
     ctx->max_pairs = pairs < ctx->sm_count / 2 ? pairs : ctx->sm_count / 2;
-    // Flags of the tiles that are cut along K (schedule.cuh): all zero between launches.
-    const size_t flag_bytes = kSkRegions * kSkFlagWordsPerRegion * sizeof(unsigned);
-    void* flags = nullptr;
-    if (cudaMalloc(&flags, flag_bytes) != cudaSuccess || cudaMemset(flags, 0, flag_bytes) != cudaSuccess) {
-        cudaGetLastError();
-        return INT4L_ERR_CUDA;
-    }
-    ctx->sk_flags = static_cast<unsigned*>(flags);
-    ctx->sk_flag_bytes = flag_bytes;
     return INT4L_OK;
 }
 
@@ -592,17 +543,14 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
     // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile
     // re-expands X less often per output, a narrower one fills more SMs when the problem is small.
-    // The schedule's own estimate of the busiest worker's time (whole waves plus the K-cut or
-    // half-width tail) stands in for the wave count.
-    const int kb_count = (p.k + 127) / 128;
-    const int tail = tail_mode();
-    const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr && ctx->sk_flags != nullptr;
+    // The schedule's own estimate of the busiest worker's time (whole waves plus a half-width
+    // tail) stands in for the wave count.
     auto waves = [&](int tile_m, int bn, int workers, bool can_halve) {
         double c = 0.0;
-        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, kb_count, workers, can_add, can_halve, &c);
+        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, workers, can_halve, &c);
         return c;
     };
-    const double cost_pairs = p.m > 128 ? waves(256, 256, ctx->max_pairs, tail < 0 || tail == 1)
+    const double cost_pairs = p.m > 128 ? waves(256, 256, ctx->max_pairs, tail_mode() != 0)
                                         : 1e30;  // a lone row block would leave CTA 1 idle
     // Tile times relative to the pair tile, from CUDA-graph replays (no launch overhead in the
     // figures) at K = 1024 and 4096: 128 x 256 on one CTA 1.7, 128 x 128 1.1, 128 x 64 0.9.

@@ -151,39 +151,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// ------------------------------------------------- flags in global memory --
-
-// One-way hand-over between two CTAs of the same grid: the producer's earlier writes (ordinary
-// stores, or bulk stores it has waited for) become visible to whoever sees the flag non-zero.
-__device__ __forceinline__ void flag_raise(unsigned* flag) {
-    asm volatile("fence.proxy.async;" ::: "memory");  // bulk-copy writes before the generic-proxy release
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
-}
-// Whole-warp call; lane 0 polls.  Bounded like mbar_wait: false (and *abort_flag raised) when the
-// flag stays zero for the whole budget or another role has already given up.
-__device__ __forceinline__ bool flag_wait(const unsigned* flag, volatile int* abort_flag, int lane,
-                                          uint64_t budget_ns = 1000ull * 1000ull * 1000ull) {
-    int ok = 1;
-    if (lane == 0) {
-        uint64_t t0 = 0;
-        for (uint32_t spin = 0;; ++spin) {
-            unsigned v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (v != 0) break;
-            if ((spin & 15u) == 15u) {
-                if (*abort_flag) { ok = 0; break; }
-                const uint64_t now = global_timer_ns();
-                if (t0 == 0) t0 = now;
-                else if (now - t0 > budget_ns) { *abort_flag = 1; ok = 0; break; }
-            }
-            __nanosleep(64);
-        }
-        asm volatile("fence.proxy.async;" ::: "memory");  // later bulk reductions after the acquire
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    return ok != 0;
-}
-
 // ------------------------------------------------------------------ fences --
 
 // Orders this thread's generic-proxy shared-memory writes before later
@@ -220,14 +187,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-        ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1)
-        : "memory");
-}
-// The same as a reduction: every int32 of the box is ADDED to the element in global memory
-// (performed at the L2 as an atomic add; boxes from different CTAs may overlap in time).
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
-    asm volatile(
-        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1)
         : "memory");
 }

@@ -480,8 +480,8 @@ def _lib_for_args():
 @pytest.mark.parametrize("m", [33, 64, 96, 128])
 @pytest.mark.parametrize("n,k", [(264, 1024), (264, 4096), (14336, 1024), (14336, 4096)])
 def test_a_few_dozen_rows(cuda, m, n, k):
-    """33 <= M <= 128 (a batch of decode requests, a short prefill): one row block of tiles whose
-    K range the schedule cuts across the SMs.  Automatic dispatch and the forced tile widths."""
+    """33 <= M <= 128 (a batch of decode requests, a short prefill): a single row block of tiles.
+    Automatic dispatch and the forced tile widths."""
     x, w, xp, wp = make_case(m, n, k, seed=17)
     ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
     assert L.path_for(m, n, k) == L.PATH_TCGEN05
