@@ -49,9 +49,13 @@ def shard_rows(w_packed, shard: Shard):
     return w_packed[shard.row_start:shard.row_start + shard.rows]
 
 
-def forward_local(x_packed, w_shard_packed, k: int | None = None, out=None):
-    """This rank's columns of Y: the single-GPU operator on its shard (asynchronous)."""
-    from .linear import linear
+def forward_local(x_packed, w_shard_packed, k: int | None = None, out=None, w_expanded=None):
+    """This rank's columns of Y: the single-GPU operator on its shard (asynchronous).  With
+    `w_expanded` (the shard expanded once by prepare_weights) and more than 128 rows of X the
+    weights skip the in-kernel unpack."""
+    from .linear import linear, linear_prepared
+    if w_expanded is not None and x_packed.shape[0] > 128 and w_shard_packed.shape[0] > 0:
+        return linear_prepared(x_packed, w_expanded, out=out)
     return linear(x_packed, w_shard_packed, k=k, out=out)
 
 
@@ -90,9 +94,14 @@ def gather_columns(y_local, n: int, group=None, align: int = 256):
 
 
 class ShardedInt4Linear:
-    """A weight-stationary N-sharded layer: holds this rank's rows of W on its GPU."""
+    """A weight-stationary N-sharded layer: holds this rank's rows of W on its GPU.
 
-    def __init__(self, w_shard_packed, n_total: int, k: int, group=None, align: int = 256):
+    expand_weights (default on): the shard is also kept expanded to bytes (twice the packed size,
+    made on the first compute-bound call), and calls with more than 128 rows of X run with it:
+    the weights then skip the in-kernel unpack, 4-5 % faster on 8192-class shapes.  Calls with
+    few rows (decode) always use the packed weights, which is what they are bound by."""
+
+    def __init__(self, w_shard_packed, n_total: int, k: int, group=None, align: int = 256, expand_weights: bool = True):
         import torch.distributed as dist
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -102,6 +111,8 @@ class ShardedInt4Linear:
             raise ValueError("weight shard has the wrong number of rows for this rank")
         self.w = w_shard_packed
         self.n_total, self.k, self.align = n_total, k, align
+        self.expand_weights = expand_weights
+        self._w_expanded = None
 
         self._fused = {}  # m -> FusedGatherBuffer
 
@@ -118,7 +129,10 @@ class ShardedInt4Linear:
             if buf is None:
                 buf = self._fused[m] = FusedGatherBuffer(m, self.n_total, x_packed.device, self.group)
             return buf.run(x_packed, self.w, self.shard, self.k)
-        y = forward_local(x_packed, self.w, self.k)
+        if self.expand_weights and self._w_expanded is None and x_packed.shape[0] > 128 and self.shard.rows > 0:
+            from .linear import prepare_weights
+            self._w_expanded = prepare_weights(self.w, self.k)
+        y = forward_local(x_packed, self.w, self.k, w_expanded=self._w_expanded)
         if gather and self.world > 1:
             return gather_columns(y, self.n_total, self.group, self.align)
         return y

@@ -100,3 +100,27 @@ def test_gather_two_gpus():
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "GATHER_OK" in out.stdout
+
+
+def test_sharded_layer_with_and_without_expanded_weights(cuda):
+    """One rank: the layer's default (weights also kept expanded, used for more than 128 rows of X)
+    and the packed-only form give the same bits as the oracle, for a prefill and a decode call."""
+    import numpy as np
+    import torch
+    import int4linear_b200 as L
+    from int4linear_b200.sharding import ShardedInt4Linear
+    from oracle import oracle as O
+    n, k = 520, 512
+    w = L.uniform_s4(0x7B02, n, k)
+    wd = torch.from_numpy(L.pack_bytes(w)).to(cuda)
+    for m in (300, 16):
+        x = L.uniform_s4(0x7B01 + m, m, k)
+        xd = torch.from_numpy(L.pack_bytes(x)).to(cuda)
+        want = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
+        for expand in (True, False):
+            layer = ShardedInt4Linear(wd, n, k, expand_weights=expand)
+            y = layer.forward(xd)
+            torch.cuda.synchronize()
+            assert O.is_same(y.cpu().numpy(), want), (m, expand)
+            assert (layer._w_expanded is not None) == (expand and m > 128)
+    assert L.last_status() == 0
