@@ -110,7 +110,7 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile
             if (*abort_flag) return false;
             uint64_t now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
+            if (t0 == 0 || now < t0) t0 = now;  /* restart the budget if the timer steps back */
             else if (now - t0 > 1000000000ull) { *abort_flag = 1; return false; }
         }
     }

@@ -145,7 +145,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if ((spin & 63u) == 63u) {
             if (*abort_flag) return false;
             uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
+            if (t0 == 0 || now < t0) t0 = now;  // (the timer is not promised to be monotonic: restart the budget if it steps back)
             else if (now - t0 > budget_ns) { *abort_flag = 1; return false; }
         }
     }
