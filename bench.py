@@ -720,11 +720,25 @@ def main():
             L.linear_host(xn, wn, k, out=yn)
         torch.cuda.synchronize()
         dt = max_over_ranks(time.perf_counter() - t0) / e2e_steps
+        # The legs by themselves, all ranks at once: what the host's links give N ranks together.
+        xdev, ydev = torch.empty_like(xd), torch.empty_like(yd)
+        legs = {}
+        for name, fn in (("h2d_x", lambda: xdev.copy_(xh, non_blocking=True)), ("d2h_y", lambda: yh.copy_(ydev, non_blocking=True))):
+            fn()
+            barrier()
+            l0 = time.perf_counter()
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            legs[name + "_ms"] = max_over_ranks(time.perf_counter() - l0) / 3 * 1e3
+        legs["h2d_x_gbs_all_ranks"] = xp.nbytes * world / (legs["h2d_x_ms"] * 1e-3) / 1e9
+        legs["d2h_y_gbs_all_ranks"] = yn.nbytes * world / (legs["d2h_y_ms"] * 1e-3) / 1e9
+        del xdev, ydev
         e2e = {"value": (ops / dt / 1e12) if bound == "tensor" else (alg_bytes_local * world / dt / 1e9),
                "unit": "TOPS" if bound == "tensor" else "GB/s",
                "h2d_bytes_per_step": int(xp.nbytes + wp.nbytes), "d2h_bytes_per_step": int(yn.nbytes),
                "ms_per_step": dt * 1e3, "steps": e2e_steps,
-               "host_numa": numa_info,
+               "host_numa": numa_info, "legs_alone": legs,
                "note": "per rank: X and this rank's rows of W uploaded from pinned host memory and this rank's "
                        "columns of Y downloaded, every step; max over ranks"}
 
