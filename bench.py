@@ -404,6 +404,51 @@ def quick_config(torch, L, dev, flush, name, int8_peak, hbm_peak, launches=5):
     return out
 
 
+SWEEP_SHAPES = ["1024x1024x1024", "2048x2048x2048", "2048x2048x1024", "512x4096x4096", "256x8192x4096",
+                "1024x4096x1024", "128x14336x4096", "64x14336x4096", "4096x4096x4096", "4096x1024x4096",
+                "3072x3072x3072", "1536x6144x2048", "8192x1024x1024"]
+
+
+def tile_sweep(shapes, launches=40):
+    """Times the tile configurations of the tensor-memory GEMM (CTA pairs; single-CTA tiles 256, 128
+    and 64 columns wide; the dispatcher's own choice) on the given MxNxK shapes, each as a CUDA graph of
+    `launches` launches over rotating operand sets larger than L2.  The relative tile times are what
+    the dispatcher's cost model (launch_tcgen05 in csrc/gemm_tcgen05.cu) is fitted to.  Prints one JSON
+    line: {"tile_sweep_us": {shape: {config: microseconds per launch}}}."""
+    import torch
+    import int4linear_b200 as L
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    configs = {"auto": (0, -1), "pairs": (0, 1), "c256": (256, 0), "c128": (128, 0), "c64": (64, 0)}
+    table = {}
+    for shape in shapes:
+        m, n, k = (int(v) for v in shape.lower().split("x"))
+        nbytes = m * k // 2 + n * k // 2 + 4 * m * n
+        sets = min(64, int(2 * L2_BYTES // nbytes) + 1)
+        xs = [device_operands(torch, dev, m, k, 1 + i) for i in range(sets)]
+        ws = [device_operands(torch, dev, n, k, 101 + i) for i in range(sets)]
+        ys = [torch.empty((m, n), dtype=torch.int32, device=dev) for _ in range(sets)]
+        row = {}
+        try:
+            for name, (tile, pairs) in configs.items():
+                if name == "pairs" and m <= 128:
+                    continue  # a lone row block would leave the second CTA of a pair idle
+                L.set_tuning(tile, False, pairs)
+                L.linear(xs[0], ws[0], out=ys[0])  # the library's first call must not happen inside a capture
+                torch.cuda.synchronize()
+                fns = [(lambda i=i: L.linear(xs[i % sets], ws[i % sets], out=ys[i % sets])) for i in range(launches)]
+                row[name] = round(graph_replay_ms(torch, L, fns) / launches * 1e3, 2)
+        finally:
+            L.set_tuning(0, False, -1)
+        best = min((v, name) for name, v in row.items() if name != "auto")
+        row["best"] = best[1]
+        row["auto_over_best"] = round(row["auto"] / best[0], 3)
+        table[shape] = row
+        del xs, ws, ys
+        torch.cuda.empty_cache()
+    print(json.dumps({"tile_sweep_us": table}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,7 +469,12 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the per-configuration figures (1 GPU)")
     ap.add_argument("--no-peak", action="store_true", help="skip the int8 tensor-rate measurement")
     ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of Y (N > 1)")
+    ap.add_argument("--tile-sweep", nargs="*", metavar="MxNxK", default=None,
+                    help="instead of the benchmark: time every tile configuration on these shapes (1 GPU)")
     args = ap.parse_args()
+    if args.tile_sweep is not None:
+        tile_sweep(args.tile_sweep or SWEEP_SHAPES)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
