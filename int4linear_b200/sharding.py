@@ -96,12 +96,14 @@ def gather_columns(y_local, n: int, group=None, align: int = 256):
 class ShardedInt4Linear:
     """A weight-stationary N-sharded layer: holds this rank's rows of W on its GPU.
 
-    expand_weights (default on): the shard is also kept expanded to bytes (twice the packed size,
+    expand_weights (default off): the shard is also kept expanded to bytes (twice the packed size,
     made on the first compute-bound call), and calls with more than 128 rows of X run with it:
-    the weights then skip the in-kernel unpack, 4-5 % faster on 8192-class shapes.  Calls with
-    few rows (decode) always use the packed weights, which is what they are bound by."""
+    the weights then skip the in-kernel unpack.  Measured on one B200 in one run: +3 % at
+    8192 x 8192 x 8192, -2.5 % at 8192 x 28672 x 8192, -3 to -6 % at 4096^3 (the expanded weights
+    double the bytes TMA moves), so it is a per-layer choice.  Calls with few rows (decode) always
+    use the packed weights, which is what they are bound by."""
 
-    def __init__(self, w_shard_packed, n_total: int, k: int, group=None, align: int = 256, expand_weights: bool = True):
+    def __init__(self, w_shard_packed, n_total: int, k: int, group=None, align: int = 256, expand_weights: bool = False):
         import torch.distributed as dist
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1

@@ -103,8 +103,8 @@ def test_gather_two_gpus():
 
 
 def test_sharded_layer_with_and_without_expanded_weights(cuda):
-    """One rank: the layer's default (weights also kept expanded, used for more than 128 rows of X)
-    and the packed-only form give the same bits as the oracle, for a prefill and a decode call."""
+    """One rank: the layer with its weights also kept expanded (used for more than 128 rows of X)
+    and the packed-only default give the same bits as the oracle, for a prefill and a decode call."""
     import numpy as np
     import torch
     import int4linear_b200 as L
