@@ -461,7 +461,7 @@ def main():
     ap.add_argument("--variant", default="default", choices=["default", "two-pass", "prepared"],
                     help="opt-in variants of the tensor-memory path: expand pre-pass + byte GEMM, weights "
                          "pre-expanded outside the timed region")
-    ap.add_argument("--tail", default="auto", choices=["auto", "none", "half"],
+    ap.add_argument("--tail", default="auto", choices=["auto", "none", "half", "kcut"],
                     help="how a last, partial wave of tiles is run (int4_linear_set_tail)")
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
@@ -530,7 +530,7 @@ def main():
     numa_info = numa.bind_to_gpu_node(bus) if bus else {"node": None, "cpus": 0, "bound": False}
     L.set_path({"auto": L.PATH_AUTO, "tcgen05": L.PATH_TCGEN05, "legacy": L.PATH_LEGACY,
                 "skinny": L.PATH_SKINNY}[args.path])
-    L.set_tail({"auto": -1, "none": 0, "half": 1}[args.tail])
+    L.set_tail({"auto": -1, "none": 0, "half": 1, "kcut": 2}[args.tail])
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -625,16 +625,30 @@ def main():
     # Second figure for the tensor-bound shapes: the same K launches back to back, no flush between
     # them (meaningful only where operands + result exceed L2, as the layers of a model would run).
     back_to_back = None
+    b2b_note = "same launches without the L2 flush between them; working set > 2 x L2"
     ws_bytes = m * k // 2 + n_local * k // 2 + 4 * m * n_local
-    if not rotate and ws_bytes > 2 * L2_BYTES:
+    if not rotate and w_prepared is None:
+        # Working sets that fit twice into L2 (the shards of a strong-scaled run) rotate over enough
+        # copies of X, W and Y to exceed it, so that no launch finds its operands cached.
+        sets = 1 if ws_bytes > 2 * L2_BYTES else int(2 * L2_BYTES // ws_bytes) + 1
+        if sets > 1:
+            b2b_note = f"launches back to back over {sets} rotating sets of X, W and Y ({sets * ws_bytes >> 20} MiB > L2), no flush"
+        xs = [xd] + [xd.clone() for _ in range(sets - 1)]
+        ws_ = [wd] + [wd.clone() for _ in range(sets - 1)]
+        ys = [yd] + [torch.empty_like(yd) for _ in range(sets - 1)]
+        reps = max(args.steps, 2 * sets)
+        for i in range(sets):
+            L.linear(xs[i], ws_[i], out=ys[i])
         b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         flush.zero_()
+        barrier()
         b0.record()
-        for i in range(args.steps):
-            step(i)
+        for i in range(reps):
+            L.linear(xs[i % sets], ws_[i % sets], out=ys[i % sets])
         b1.record()
         barrier()
-        back_to_back = max_over_ranks(b0.elapsed_time(b1) / args.steps)
+        back_to_back = max_over_ranks(b0.elapsed_time(b1) / reps)
+        del xs, ws_, ys
     # Microsecond-scale tensor shapes (c1): one launch is comparable with the launch overhead an
     # event pair sees, so the K launches are also timed as one CUDA-graph replay over rotating
     # copies of X, W and Y that together exceed L2.
@@ -856,7 +870,7 @@ def main():
         line["graph_replay"] = graph_replay
     if back_to_back is not None:
         line["back_to_back"] = {"ms_per_step": back_to_back, "value": ops / (back_to_back * 1e-3) / 1e12,
-                                "unit": "TOPS", "note": "same launches without the L2 flush between them; working set > 2 x L2"}
+                                "unit": "TOPS", "note": b2b_note}
     if strong_c5 is not None:
         line["strong_c5"] = strong_c5
     if gather_check is not None:

@@ -251,10 +251,14 @@ int int4_linear_set_path(int path);
 int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
 
 /* How the tensor-memory kernels run a last wave of output tiles that does not fill the GPU:
- * -1 (default) and 1: as half-width items when at most half of the CTA pairs would be busy
- * (about three quarters of a tile time instead of a whole one); 0: as whole tiles.  The results
- * are identical.  Replaces the fixed one-CTA-per-tile grid of kernels/linear_v21.cu:20-37.
- * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_TAIL=none|half. */
+ * 0 as whole tiles; 1 as half-width items when at most half of the CTA pairs would be busy (about
+ * three quarters of a tile time instead of a whole one); 2 cut along K into equal shares for all
+ * workers, every share ADDING its partial sums into Y (bulk reductions; integer addition, so the
+ * result is bit-identical whatever the order) after a small kernel, launched in front of the GEMM
+ * on the same stream, has cleared those tiles; -1 (default) whichever of the three the schedule's
+ * cost estimate prefers.  Mode 2 applies to int32 output on one GPU.  The results are identical in
+ * all modes.  Replaces the fixed one-CTA-per-tile grid of kernels/linear_v21.cu:20-37.
+ * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_TAIL=none|half|kcut. */
 int int4_linear_set_tail(int mode);
 
 /* Overlap of back-to-back decode-shape launches in one stream (programmatic dependent

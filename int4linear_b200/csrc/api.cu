@@ -136,6 +136,7 @@ int tail_mode()
         v = -1;
         if (e && !std::strcmp(e, "none")) v = 0;
         else if (e && !std::strcmp(e, "half")) v = 1;
+        else if (e && !std::strcmp(e, "kcut")) v = 2;
         g_tail.store(v);
     }
     return v;
@@ -688,7 +689,7 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
 
 int int4_linear_set_tail(int mode)
 {
-    if (mode < -1 || mode > 1) return INT4L_ERR_INVALID_ARG;
+    if (mode < -1 || mode > 2) return INT4L_ERR_INVALID_ARG;
     g_tail.store(mode);
     return INT4L_OK;
 }

@@ -152,7 +152,7 @@ bool getenv_flag_direct_store();
 int forced_tile_n();
 int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
 int two_pass_mode();  // -1 automatic, 0 never, 1 whenever the tensor-memory family is used
-int tail_mode();  // int4_linear_set_tail: -1 automatic, 0 whole tiles only, 1 half-width items
+int tail_mode();  // int4_linear_set_tail: -1 automatic, 0 whole tiles only, 1 half-width items, 2 cut along K
 int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always (m > 128)
 
 }  // namespace i4l

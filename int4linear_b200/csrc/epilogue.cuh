@@ -19,7 +19,9 @@
 
 namespace i4l {
 
-template <bool kTmaStore>
+// kAdd: the values are partial sums of a tile that is cut along K and are ADDED into Y (a bulk
+// reduction per staged block, or atomic adds on the per-thread path) instead of stored.
+template <bool kTmaStore, bool kAdd = false>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, int row0, int col0, int m, int n,
                                                   int* __restrict__ y, const int* __restrict__ bias,
                                                   const CUtensorMap* tm_y, int n_maps, int col_shift,
@@ -57,7 +59,9 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
             if (lane == 0) {
                 // One store per destination matrix (one normally; every rank's copy of the full Y
                 // when the result is gathered through peer memory), all from the same staging tile.
-                for (int d = 0; d < n_maps; ++d) tma_store_2d(tm_y + d, stg, col_shift + col0 + c, row0);
+                if constexpr (kAdd) tma_reduce_add_2d(tm_y, stg, col_shift + col0 + c, row0);
+                else
+                    for (int d = 0; d < n_maps; ++d) tma_store_2d(tm_y + d, stg, col_shift + col0 + c, row0);
                 tma_store_commit();
             }
             ++chunk_no;
@@ -67,7 +71,11 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int col = col0 + c + 4 * q;
-                    if (vec_ok && col + 3 < n) {
+                    if constexpr (kAdd) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (col + e < n) atomicAdd(dst + 4 * q + e, static_cast<int>(v[4 * q + e]));
+                    } else if (vec_ok && col + 3 < n) {
                         *reinterpret_cast<int4*>(dst + 4 * q) =
                             make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     } else {

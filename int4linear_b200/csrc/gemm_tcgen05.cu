@@ -171,19 +171,8 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         if constexpr (CTAS == 2) cluster_wait();
     }
 
-    // Every role walks the same list of items (schedule.cuh): whole tiles, then half-width items.
-    const int tiles_m = sched.tiles_m, tiles_n = sched.tiles_n;
-    const int kb_count = (k + 127) / 128;
-    constexpr int kGroupM = 16;  // tiles of 16 consecutive M blocks share their W panel in L2
-    auto tile_coord = [&](int tile, int& tm, int& tn) {
-        const int group_size = kGroupM * tiles_n;
-        const int group = tile / group_size;
-        const int first_m = group * kGroupM;
-        const int gm = min(tiles_m - first_m, kGroupM);
-        const int in_group = tile - group * group_size;
-        tm = first_m + in_group % gm;
-        tn = in_group / gm;
-    };
+    // Every role walks the same list of segments (schedule.cuh): whole tiles, then half-width
+    // items or the K ranges of the tiles that are cut along K.
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
@@ -193,9 +182,9 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             Segment sg;
             for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si) {
                 int tm, tn;
-                tile_coord(sg.tile, tm, tn);
+                tile_coord(sched, sg.tile, &tm, &tn);
                 const int rows_w = sg.width / CTAS;
-                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % P, r = it / P;
                     if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                     mbar_expect_tx(pk_full(s), C::kPreW ? C::kPkStage : (kBM + rows_w) * kBKBytes);
@@ -230,7 +219,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 if (!mbar_wait(tm_empty(buf), (br & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kb_count; ++kb, ++it) {
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % U, r = it / U;
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
                     tc_fence_after_sync();
@@ -240,7 +229,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // 32 bytes of K per instruction: advance the start address field by 32 >> 4.
-                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u);
+                        umma_i8<CTAS>(d_tmem, a_desc + 2u * j, b_desc + 2u * j, idesc, (kb != sg.kb0 || j != 0) ? 1u : 0u);
                     }
                     if constexpr (CTAS == 2) umma_commit_2cta(up_empty(s), 3); else umma_commit(up_empty(s));
                 }
@@ -260,7 +249,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         Segment sg;
         for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si, ++local_tile) {
             int tm, tn;
-            tile_coord(sg.tile, tm, tn);
+            tile_coord(sched, sg.tile, &tm, &tn);
             const int col_off = sg.col_off, width = sg.width;
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
             if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
@@ -275,8 +264,13 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                     else drain_accumulator_scaled_tma<false>(t_addr, width, row0, col0, m, n, so, y_maps, stage0, chunk_no, lane);
                 }
                 else drain_accumulator_scaled(t_addr, width, row0, col0, m, n, so, lane);
+            } else if (sg.mode != kSegStore) {
+                // A share of a tile that is cut along K: added into Y, which the clearing kernel in
+                // front of this launch has zeroed; the share that holds K block 0 brings the bias.
+                drain_accumulator<kTmaStore, true>(t_addr, width, row0, col0, m, n, y, sg.mode == kSegAddFirst ? bias : nullptr,
+                                                   y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
             } else {
-                drain_accumulator<kTmaStore>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
+                drain_accumulator<kTmaStore, false>(t_addr, width, row0, col0, m, n, y, bias, y_maps, n_y_maps, col_shift, stage0, chunk_no, lane);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -308,7 +302,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si) {
             // 16-byte chunks to convert in this item's stages (a half-width item has fewer W rows)
             const int chunks = C::kPreW ? kChunks : (sg.width == BN ? kChunks : (kBM + C::kRowsW / 2) * 4);
-            for (int kb = 0; kb < kb_count; ++kb, ++it) {
+            for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
@@ -399,6 +393,31 @@ gemm_s4_tcgen05_gather_kernel(const __grid_constant__ CUtensorMap tm_x,
                                   status, bias, ScaledOut{});
 }
 
+// Clears the tiles the next GEMM launch cuts along K (its shares only add into them).  One block per
+// tile, whole 16-byte stores where the row pitch allows; rows and columns beyond Y are skipped.
+__global__ void __launch_bounds__(256)
+clear_cut_tiles_kernel(int* __restrict__ y, int m, int n, const Schedule sched, int tile_m, int bn)
+{
+    int tm, tn;
+    tile_coord(sched, sched.whole + static_cast<int>(blockIdx.x), &tm, &tn);
+    const int row0 = tm * tile_m, col0 = tn * bn;
+    const int rows = min(tile_m, m - row0), cols = min(bn, n - col0);
+    if (rows <= 0 || cols <= 0) return;
+    const bool vec_ok = (n & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && (cols & 3) == 0;
+    if (vec_ok) {
+        const int per_row = cols >> 2;
+        for (int i = threadIdx.x; i < rows * per_row; i += blockDim.x) {
+            const int r = i / per_row, c = (i - r * per_row) << 2;
+            *reinterpret_cast<int4*>(y + static_cast<size_t>(row0 + r) * n + col0 + c) = make_int4(0, 0, 0, 0);
+        }
+    } else {
+        for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
+            const int r = i / cols, c = i - r * cols;
+            y[static_cast<size_t>(row0 + r) * n + col0 + c] = 0;
+        }
+    }
+}
+
 using Cfg256 = Cfg<256, 3, 2, 1>;
 using Cfg128 = Cfg<128, 4, 3, 1>;
 using Cfg64 = Cfg<64, 4, 4, 1>;
@@ -429,15 +448,23 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     } else {
         tm_y = tm_x;  // unused by the kernel
     }
-    // A last wave of tiles that would keep at most half of the CTA pairs busy is issued as
-    // half-width items (schedule.cuh).
+    // The last, partial wave of tiles: cut along K where partial sums can be added into Y (int32
+    // output on this GPU) and that is cheaper, else as half-width items, else whole (schedule.cuh).
     const int max_workers = C::kCtas == 2 ? ctx->max_pairs : ctx->sm_count;
-    const bool can_halve = tail_mode() != 0 && !C::kPreW && C::kCtas == 2;
-    const Schedule sched = plan_schedule(tiles_m, tiles_n, max_workers, can_halve);
+    const int tail = tail_mode();
+    const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr && gather == nullptr;
+    const bool can_halve = (tail < 0 || tail == 1) && !C::kPreW && C::kCtas == 2;
+    const Schedule sched = plan_schedule(tiles_m, tiles_n, (p.k + 127) / 128, max_workers, can_add, can_halve, nullptr, tail == 2);
     tm_wh = tm_x;  // unused unless tiles are halved
     if (sched.half_tiles > 0) {
         rc = make_tensor_map_2d(ctx, &tm_wh, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW / 2, false);
         if (rc != INT4L_OK) return rc;
+    }
+    if (sched.sk_tiles > 0) {
+        // The cut tiles only receive additions: clear them first, on the same stream.
+        clear_cut_tiles_kernel<<<sched.sk_tiles, 256, 0, stream>>>(static_cast<int*>(p.y), p.m, p.n, sched, C::kTileM, C::kBN);
+        count_launch();
+        if (cudaGetLastError() != cudaSuccess) return INT4L_ERR_CUDA;
     }
     const int workers = sched.workers;
     cudaLaunchConfig_t cfg = {};
@@ -543,14 +570,17 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
     // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile
     // re-expands X less often per output, a narrower one fills more SMs when the problem is small.
-    // The schedule's own estimate of the busiest worker's time (whole waves plus a half-width
-    // tail) stands in for the wave count.
+    // The schedule's own estimate of the busiest worker's time (whole waves plus the K-cut or
+    // half-width tail) stands in for the wave count.
+    const int kb_count = (p.k + 127) / 128;
+    const int tail = tail_mode();
+    const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr;
     auto waves = [&](int tile_m, int bn, int workers, bool can_halve) {
         double c = 0.0;
-        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, workers, can_halve, &c);
+        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, kb_count, workers, can_add, can_halve, &c, tail == 2);
         return c;
     };
-    const double cost_pairs = p.m > 128 ? waves(256, 256, ctx->max_pairs, tail_mode() != 0)
+    const double cost_pairs = p.m > 128 ? waves(256, 256, ctx->max_pairs, tail < 0 || tail == 1)
                                         : 1e30;  // a lone row block would leave CTA 1 idle
     // Tile times relative to the pair tile, from CUDA-graph replays (no launch overhead in the
     // figures) at K = 1024 and 4096: 128 x 256 on one CTA 1.7, 128 x 128 1.1, 128 x 64 0.9.

@@ -190,6 +190,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src,
         ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1)
         : "memory");
 }
+// The same as a reduction: every int32 of the box is ADDED to the element in global memory
+// (performed at the L2 as an atomic add; boxes from different CTAs may overlap in time).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t src, int c0, int c1) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1)
+        : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -301,7 +301,7 @@ def set_two_pass(mode: int) -> int:
 
 
 def set_tail(mode: int) -> None:
-    """-1 automatic, 0 whole tiles, 1 half-width items for a short last wave (int4_linear_set_tail)."""
+    """-1 automatic, 0 whole tiles, 1 half-width items, 2 last wave cut along K (int4_linear_set_tail)."""
     st = _lib.load().int4_linear_set_tail(mode)
     if st != 0:
         raise Int4LinearError(st, "int4_linear_set_tail")

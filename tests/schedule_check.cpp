@@ -1,7 +1,9 @@
 // CPU check of the tile schedule of the persistent GEMM kernels (int4linear_b200/csrc/schedule.cuh):
-// for many (tiles, workers) combinations every tile must be covered exactly once -- whole, or by
-// its two half-width items -- and no worker may be handed more than its share.
-// Prints "SCHEDULE_OK <cases>".
+// for many (tiles, K blocks, workers) combinations every K block of every tile must be computed
+// exactly once; a tile that is cut along K must have exactly one segment that starts at K block 0
+// (the one that brings the bias) and all of its segments must add; whole tiles and half-width items
+// must store; the half-width items of a tile must cover its two halves; no worker may get more than
+// two partial segments.  Prints "SCHEDULE_OK <cases>".
 #include <cstdio>
 #include <vector>
 
@@ -9,32 +11,56 @@
 
 using namespace i4l;
 
-static int check(int tiles_m, int tiles_n, int workers, bool can_halve)
+static int check(int tiles_m, int tiles_n, int kb, int workers, bool can_add, bool can_halve)
 {
     const int bn = 256;
     double cost = 0.0;
-    const Schedule s = plan_schedule(tiles_m, tiles_n, workers, can_halve, &cost);
+    const Schedule s = plan_schedule(tiles_m, tiles_n, kb, workers, can_add, can_halve, &cost);
     const int tiles = tiles_m * tiles_n;
-    if (s.whole + s.half_tiles != tiles) return 1;
-    if (s.workers < 1 || s.workers > workers) return 2;
-    if (!can_halve && s.half_tiles) return 3;
-    std::vector<int> cover(static_cast<size_t>(tiles) * 2, 0);  // [tile][half]
-    int busiest = 0;
+    if (s.whole + s.half_tiles + s.sk_tiles != tiles) return 1;
+    if (s.half_tiles && s.sk_tiles) return 2;
+    if (s.workers < 1 || s.workers > workers) return 3;
+    if ((!can_add && s.sk_tiles) || (!can_halve && s.half_tiles)) return 4;
+    std::vector<int> cover(static_cast<size_t>(tiles) * kb * 2, 0);  // [tile][kb][half]
+    std::vector<int> firsts(tiles, 0), adds(tiles, 0), stores(tiles, 0);
     for (int w = 0; w < s.workers; ++w) {
         Segment g;
-        int i = 0;
-        for (; segment_of(s, w, bn, i, &g); ++i) {
-            if (g.tile < 0 || g.tile >= tiles) return 4;
-            if (g.width == bn) { if (g.col_off != 0) return 5; ++cover[g.tile * 2]; ++cover[g.tile * 2 + 1]; }
-            else if (g.width == bn / 2 && (g.col_off == 0 || g.col_off == bn / 2)) ++cover[g.tile * 2 + (g.col_off ? 1 : 0)];
-            else return 6;
-            if (i > 1000000) return 7;
+        int partial = 0;
+        for (int i = 0; segment_of(s, w, bn, i, &g); ++i) {
+            if (g.tile < 0 || g.tile >= tiles || g.kb0 < 0 || g.kb1 > kb || g.kb0 >= g.kb1) return 5;
+            if (g.width != bn && g.width != bn / 2) return 6;
+            if (g.mode == kSegStore) {
+                ++stores[g.tile];
+                if (g.kb0 != 0 || g.kb1 != kb || g.tile >= s.whole + s.half_tiles) return 7;
+            } else {
+                ++partial;
+                ++adds[g.tile];
+                if (g.tile < s.whole || g.width != bn || g.col_off != 0) return 8;
+                if ((g.mode == kSegAddFirst) != (g.kb0 == 0)) return 9;
+                if (g.mode == kSegAddFirst) ++firsts[g.tile];
+            }
+            for (int b = g.kb0; b < g.kb1; ++b)
+                for (int h = 0; h < 2; ++h)
+                    if (g.width == bn || g.col_off == h * (bn / 2)) ++cover[(static_cast<size_t>(g.tile) * kb + b) * 2 + h];
+            if (i > 1000000) return 10;
         }
-        if (i > busiest) busiest = i;
+        if (partial > 2) return 11;
     }
-    for (int v : cover) if (v != 1) return 8;
-    if (busiest > (tiles + workers - 1) / workers + 1) return 9;
-    if (cost <= 0.0 || cost > busiest + 1e-9) return 10;
+    for (int v : cover) if (v != 1) return 12;
+    for (int t = 0; t < tiles; ++t) {
+        if (adds[t] > 0 && (firsts[t] != 1 || stores[t] != 0)) return 13;
+        if (adds[t] == 0 && firsts[t] != 0) return 14;
+    }
+    if (cost <= 0.0) return 15;
+    // the raster must be a bijection between tile indices and (row block, column block)
+    std::vector<int> seen(tiles, 0);
+    for (int t = 0; t < tiles; ++t) {
+        int tm, tn;
+        tile_coord(s, t, &tm, &tn);
+        if (tm < 0 || tm >= tiles_m || tn < 0 || tn >= tiles_n) return 16;
+        ++seen[tm * tiles_n + tn];
+    }
+    for (int v : seen) if (v != 1) return 17;
     return 0;
 }
 
@@ -42,21 +68,30 @@ int main()
 {
     long cases = 0;
     const int worker_counts[] = {1, 2, 3, 7, 64, 66, 74, 132, 148};
+    const int kbs[] = {1, 2, 3, 4, 5, 8, 13, 32, 64, 127, 1023};
     for (int workers : worker_counts)
-        for (int tm = 1; tm <= 40; ++tm)
-            for (int tn = 1; tn <= 120; tn += (tn < 9 ? 1 : 5))
-                for (int halve = 0; halve < 2; ++halve) {
-                    const int rc = check(tm, tn, workers, halve != 0);
-                    if (rc) {
-                        std::printf("SCHEDULE_BAD rc=%d tiles=%dx%d workers=%d halve=%d\n", rc, tm, tn, workers, halve);
-                        return 1;
+        for (int kb : kbs)
+            for (int tm = 1; tm <= 40; tm += (tm < 6 ? 1 : 7))
+                for (int tn = 1; tn <= 120; tn += (tn < 9 ? 1 : 13))
+                    for (int mode = 0; mode < 4; ++mode) {
+                        const int rc = check(tm, tn, kb, workers, mode & 1, mode & 2);
+                        if (rc) {
+                            std::printf("SCHEDULE_BAD rc=%d tiles=%dx%d kb=%d workers=%d mode=%d\n", rc, tm, tn, kb, workers, mode);
+                            return 1;
+                        }
+                        ++cases;
                     }
-                    ++cases;
-                }
-    Schedule s = plan_schedule(32, 14, 74, true);   // 8192 x 3584 outputs on 74 CTA pairs: 448 = 6 * 74 + 4
-    if (s.half_tiles != 4 || s.whole != 444 || s.workers != 74) { std::printf("SCHEDULE_BAD c5 shard\n"); return 1; }
-    s = plan_schedule(32, 4, 74, true);             // 8192 x 1024: 128 = 74 + 54, too many for halving
-    if (s.half_tiles != 0 || s.whole != 128) { std::printf("SCHEDULE_BAD m8 shard\n"); return 1; }
+    // the shapes the design notes quote
+    Schedule s = plan_schedule(32, 4, 64, 74, true, true);   // 8192 x 1024 x 8192 on 74 CTA pairs: 128 = 74 + 54, the cut does not pay
+    if (s.sk_tiles != 0 || s.half_tiles != 0 || s.whole != 128) { std::printf("SCHEDULE_BAD m8 shard\n"); return 1; }
+    s = plan_schedule(32, 4, 64, 74, true, true, nullptr, true);   // ... unless it is forced
+    if (s.sk_tiles != 54 || s.whole != 74 || s.sk_workers != 74) { std::printf("SCHEDULE_BAD m8 shard, forced\n"); return 1; }
+    s = plan_schedule(32, 14, 64, 74, true, true);            // 8192 x 3584 x 8192: 448 = 6 * 74 + 4
+    if (s.sk_tiles != 4 || s.whole != 444 || s.sk_workers != 64) { std::printf("SCHEDULE_BAD c5 shard\n"); return 1; }
+    s = plan_schedule(32, 14, 64, 74, false, true);
+    if (s.half_tiles != 4 || s.sk_tiles != 0) { std::printf("SCHEDULE_BAD c5 shard, half\n"); return 1; }
+    s = plan_schedule(16, 16, 32, 74, true, true);            // 4096^3: the half-width tail is cheaper than the cut
+    if (s.half_tiles != 34 || s.sk_tiles != 0) { std::printf("SCHEDULE_BAD c2\n"); return 1; }
     std::printf("SCHEDULE_OK %ld\n", cases);
     return 0;
 }

@@ -138,9 +138,9 @@ def test_no_gpu_means_error_not_fallback():
 
 
 def test_tile_schedule_covers_every_tile_once(tmp_path):
-    """The schedule of the persistent GEMM kernels (whole tiles, half-width items) is plain
-    host/device arithmetic: tests/schedule_check.cpp enumerates it for tens of thousands of
-    (tiles, workers) combinations with the host compiler."""
+    """The schedule of the persistent GEMM kernels (whole tiles, half-width items, tiles cut along
+    K) is plain host/device arithmetic: tests/schedule_check.cpp enumerates it for tens of thousands
+    of (tiles, K blocks, workers) combinations with the host compiler."""
     import subprocess
     exe = str(tmp_path / "schedule_check")
     subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, os.path.join(ROOT, "tests", "schedule_check.cpp")], check=True)
