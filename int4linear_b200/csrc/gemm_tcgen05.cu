@@ -247,6 +247,9 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
         uint32_t chunk_no = 0;
         bool alive = true;
         Segment sg;
+        // With tiles cut along K this grid was allowed to start before the clearing kernel in front of
+        // it had finished; nothing is added into Y until that kernel has completed.
+        if (sched.sk_tiles > 0) asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int si = 0; alive && segment_of(sched, worker, BN, si, &sg); ++si, ++local_tile) {
             int tm, tn;
             tile_coord(sched, sg.tile, &tm, &tn);
@@ -398,6 +401,10 @@ gemm_s4_tcgen05_gather_kernel(const __grid_constant__ CUtensorMap tm_x,
 __global__ void __launch_bounds__(256)
 clear_cut_tiles_kernel(int* __restrict__ y, int m, int n, const Schedule sched, int tile_m, int bn)
 {
+    // The GEMM behind this kernel is launched with programmatic stream serialisation: it may start
+    // right away and run its main loops while the tiles are being cleared; its epilogue warps wait
+    // for this grid to have completed before their first addition.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int tm, tn;
     tile_coord(sched, sched.whole + static_cast<int>(blockIdx.x), &tm, &tn);
     const int row0 = tm * tile_m, col0 = tn * bn;
@@ -472,13 +479,16 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = C::kCtas;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // Behind a clearing kernel: start while it runs (the epilogue waits for it, see the kernel).
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = sched.sk_tiles > 0 ? 2 : 1;
     cudaError_t e;
     if constexpr (kTmaStore && !C::kPreW) {
         if (gather != nullptr) {

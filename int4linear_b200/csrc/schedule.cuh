@@ -35,10 +35,11 @@ namespace i4l {
 
 constexpr int kSkMinBlocks = 4;         // shortest K range worth a segment of its own
 // What the cut costs beyond its K blocks, in K blocks of main-loop time (0.39 us each for a CTA pair):
-// the clearing launch in front and two more epilogues, the last one exposed.  Measured on B200:
-// 24 (4096 x 4096 x 8192), 28 (4096^3), 33 (8192^3) -- so the cut pays only where a whole tile time of
-// 64 K blocks or more would otherwise be spent on a handful of tiles.
-constexpr int kSkSplitCostBlocks = 28;
+// two more epilogues per worker, the last one exposed, plus clearing and read-modify-write traffic
+// that grows with the number of cut tiles.  Measured on B200 with the clearing kernel overlapped
+// (programmatic dependent launch): 11 K blocks with 34 cut tiles of 74 workers (4096 x 4096 x 8192),
+// 18 (4096^3, 34 tiles), 24 (8192^3, 62 tiles).
+constexpr double kSkSplitCostBase = 8.0, kSkSplitCostPerFullWave = 20.0;
 
 struct Schedule {
     int tiles_m = 0, tiles_n = 0, kb_count = 0;
@@ -159,7 +160,8 @@ inline Schedule plan_schedule(int tiles_m, int tiles_n, int kb_count, int max_wo
         long long skw = units / kSkMinBlocks;
         if (skw > max_workers) skw = max_workers;
         const long long longest = skw > 0 ? (units + skw - 1) / skw : kb_count;
-        const double cut_cost = static_cast<double>(longest + kSkSplitCostBlocks) / kb_count;
+        const double cut_cost = (static_cast<double>(longest) + kSkSplitCostBase +
+                                 kSkSplitCostPerFullWave * rem / max_workers) / kb_count;
         // A half-width item still expands the whole X tile: about 0.75 of a tile time; a launch that
         // consists of nothing else is dominated by filling the pipeline (measured).
         const bool halvable = can_halve && 2 * rem <= max_workers;

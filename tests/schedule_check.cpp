@@ -92,6 +92,8 @@ int main()
     if (s.half_tiles != 4 || s.sk_tiles != 0) { std::printf("SCHEDULE_BAD c5 shard, half\n"); return 1; }
     s = plan_schedule(16, 16, 32, 74, true, true);            // 4096^3: the half-width tail is cheaper than the cut
     if (s.half_tiles != 34 || s.sk_tiles != 0) { std::printf("SCHEDULE_BAD c2\n"); return 1; }
+    s = plan_schedule(16, 16, 64, 74, true, true);            // 4096 x 4096 x 8192: the cut is (just) cheaper
+    if (s.sk_tiles != 34 || s.half_tiles != 0) { std::printf("SCHEDULE_BAD c3\n"); return 1; }
     std::printf("SCHEDULE_OK %ld\n", cases);
     return 0;
 }
