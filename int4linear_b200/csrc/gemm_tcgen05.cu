@@ -432,6 +432,13 @@ using Cfg256x2 = Cfg<256, 4, 4, 2>;  // 256 x 256 tile on a CTA pair (a fourth e
 using Cfg256x2W = Cfg<256, 4, 4, 2, true>;  // the same with pre-expanded weights
 using Cfg128W = Cfg<128, 4, 4, 1, true>;
 
+// Time of one K block (and so of one tile) of a tile shape relative to the 256 x 256 pair tile, from
+// CUDA-graph replays (no launch overhead in the figures) at K = 1024 and 4096.
+constexpr double block_time_of(int bn, int ctas)
+{
+    return ctas == 2 ? 1.0 : (bn == 256 ? 1.7 : (bn == 128 ? 1.1 : 0.9));
+}
+
 template <class C, bool kTmaStore>
 int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const GatherDst* gather = nullptr)
 {
@@ -461,7 +468,8 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     const int tail = tail_mode();
     const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr && gather == nullptr;
     const bool can_halve = (tail < 0 || tail == 1) && !C::kPreW && C::kCtas == 2;
-    const Schedule sched = plan_schedule(tiles_m, tiles_n, (p.k + 127) / 128, max_workers, can_add, can_halve, nullptr, tail == 2);
+    const Schedule sched = plan_schedule(tiles_m, tiles_n, (p.k + 127) / 128, max_workers, can_add, can_halve, nullptr, tail == 2,
+                                         block_time_of(C::kBN, C::kCtas));
     tm_wh = tm_x;  // unused unless tiles are halved
     if (sched.half_tiles > 0) {
         rc = make_tensor_map_2d(ctx, &tm_wh, p.w, 1, pitch, p.n, pitch, kBKBytes, C::kRowsW / 2, false);
@@ -587,16 +595,17 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     const bool can_add = (tail < 0 || tail == 2) && p.scaled.y16 == nullptr;
     auto waves = [&](int tile_m, int bn, int workers, bool can_halve) {
         double c = 0.0;
-        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, kb_count, workers, can_add, can_halve, &c, tail == 2);
+        plan_schedule((p.m + tile_m - 1) / tile_m, (p.n + bn - 1) / bn, kb_count, workers, can_add, can_halve, &c, tail == 2,
+                      block_time_of(bn, tile_m == 256 ? 2 : 1));
         return c;
     };
     const double cost_pairs = p.m > 128 ? waves(256, 256, ctx->max_pairs, tail < 0 || tail == 1)
                                         : 1e30;  // a lone row block would leave CTA 1 idle
     // Tile times relative to the pair tile, from CUDA-graph replays (no launch overhead in the
     // figures) at K = 1024 and 4096: 128 x 256 on one CTA 1.7, 128 x 128 1.1, 128 x 64 0.9.
-    const double cost256 = waves(kBM, 256, ctx->sm_count, false) * 1.7;
-    const double cost128 = waves(kBM, 128, ctx->sm_count, false) * 1.1;
-    const double cost64 = waves(kBM, 64, ctx->sm_count, false) * 0.9;
+    const double cost256 = waves(kBM, 256, ctx->sm_count, false) * block_time_of(256, 1);
+    const double cost128 = waves(kBM, 128, ctx->sm_count, false) * block_time_of(128, 1);
+    const double cost64 = waves(kBM, 64, ctx->sm_count, false) * block_time_of(64, 1);
     int bn = 256;
     double best = cost256;
     if (cost128 < best) { best = cost128; bn = 128; }
