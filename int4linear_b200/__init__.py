@@ -26,6 +26,7 @@ from .linear import (  # noqa: F401
     set_path,
     set_overlap,
     set_tail,
+    set_fewrows,
     set_two_pass,
     set_tuning,
     PATH_AUTO,

@@ -35,6 +35,7 @@ SYMBOLS = {
     "int4_linear_set_tuning": (_I, [_I, _I, _I]),
     "int4_linear_set_overlap": (_I, [_I]),
     "int4_linear_set_tail": (_I, [_I]),
+    "int4_linear_set_fewrows": (_I, [_I]),
     "int4_linear_set_two_pass": (_I, [_I]),
     "int4_linear_path_for": (_I, [_I, _I, _I]),
     "int4_linear_device_info": (_I, [_I]),

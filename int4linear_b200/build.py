@@ -18,7 +18,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libint4linear_b200.so")
-SOURCES = ["api.cu", "gemm_tcgen05.cu", "gemm_tcgen05_s8.cu", "gemm_skinny.cu", "gemm_legacy.cu", "packer.cu", "probe.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "gemm_tcgen05.cu", "gemm_tcgen05_s8.cu", "gemm_skinny.cu", "gemm_legacy.cu", "packer.cu", "probe.cu", "gemm_fewrows.cu", "no_alloc.cu"]
 
 
 def _deps() -> list[str]:

@@ -28,6 +28,7 @@ std::atomic<int> g_overlap{-1};    // -1 = not yet read from the environment
 std::atomic<int> g_two_pass{-2};   // -2 = not yet read from the environment
 std::atomic<int> g_pairs{-2};      // -2 = not yet read from the environment
 std::atomic<int> g_tail{-2};       // -2 = not yet read from the environment
+std::atomic<int> g_fewrows{-2};    // few-rows kernel (M <= 64): -1 by shape, 0 never, 1 whenever it can run
 thread_local int t_last_status = INT4L_OK;
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -142,6 +143,18 @@ int tail_mode()
     return v;
 }
 
+int fewrows_mode()
+{
+    int v = g_fewrows.load();
+    if (v == -2) {
+        const char* e = std::getenv("INT4L_FEWROWS");
+        v = e ? std::atoi(e) : -1;
+        if (v < -1 || v > 1) v = -1;
+        g_fewrows.store(v);
+    }
+    return v;
+}
+
 DeviceCtx* current_ctx(int* status)
 {
     int dev = -1;
@@ -182,6 +195,7 @@ DeviceCtx* current_ctx(int* status)
     int rc = setup_tcgen05(c);
     if (rc == INT4L_OK) rc = setup_tcgen05_s8(c);
     if (rc == INT4L_OK) rc = setup_skinny(c);
+    if (rc == INT4L_OK) rc = setup_fewrows(c);
     if (rc != INT4L_OK) { *status = rc; return nullptr; }
     c->attrs_set = true;
     g_ctx_ready[dev] = true;
@@ -234,8 +248,15 @@ int choose_path(const DeviceCtx* ctx, const Problem& p)
     const int forced = current_path();
     if (forced == INT4L_PATH_SKINNY) return skinny_supports(ctx, p) ? INT4L_PATH_SKINNY : INT4L_PATH_TCGEN05;
     if (forced != INT4L_PATH_AUTO) return forced;
-    // Measured: from m = 33 upwards the tensor-memory kernel with 128-wide tiles is at least as fast.
-    if (p.m <= 32 && skinny_supports(ctx, p)) return INT4L_PATH_SKINNY;
+    // Measured (CUDA-graph replays, weights from HBM): up to 16 rows the register kernels win; from
+    // 17 to 32 rows they still do while the weights are small (4096 x 4096: 8.3 us against 9.6), and
+    // the few-rows tensor-memory kernel wins from 32 M weight elements on (14336 x 4096: 13.0 us
+    // against 18.5); from 33 rows on the tensor-memory family always.
+    const bool fewrows_ok = fewrows_mode() != 0 && fewrows_supports(p);
+    if (fewrows_mode() == 1 && fewrows_ok) return INT4L_PATH_TCGEN05;
+    const bool large = static_cast<long long>(p.n) * p.k >= (1ll << 25);
+    const int skinny_rows = (fewrows_ok && large) ? 16 : 32;
+    if (p.m <= skinny_rows && skinny_supports(ctx, p)) return INT4L_PATH_SKINNY;
     return INT4L_PATH_TCGEN05;
 }
 
@@ -684,6 +705,13 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs)
     g_tile_n.store(tile_n);
     g_direct_store.store(direct_store ? 1 : 0);
     g_pairs.store(cta_pairs);
+    return INT4L_OK;
+}
+
+int int4_linear_set_fewrows(int mode)
+{
+    if (mode < -1 || mode > 1) return INT4L_ERR_INVALID_ARG;
+    g_fewrows.store(mode);
     return INT4L_OK;
 }
 

@@ -132,6 +132,14 @@ int launch_unpack(DeviceCtx* ctx, const void* src, void* dst, int rows, int cols
 // Read-only streaming pass over `bytes` bytes (probe.cu): the one-launch floor of the decode shapes.
 int launch_stream_read(DeviceCtx* ctx, const void* src, size_t bytes, unsigned* sink, cudaStream_t stream);
 
+// Few rows of X (M <= 64): operands swapped, W through tensor memory (gemm_fewrows.cu).
+bool fewrows_supports(const Problem& p);
+int launch_fewrows(DeviceCtx* ctx, const Problem& p, cudaStream_t stream);
+int setup_fewrows(DeviceCtx* ctx);
+// Clears the tiles a following GEMM launch cuts along K (gemm_tcgen05.cu); transposed: tiles of Y transposed.
+struct Schedule;
+int launch_clear_cut_tiles(int* y, int m, int n, const Schedule& sched, int tile_m, int bn, bool transposed, cudaStream_t stream);
+
 // One-off function attribute set-up (dynamic shared memory opt-in).
 int setup_tcgen05(DeviceCtx* ctx);
 int setup_tcgen05_s8(DeviceCtx* ctx);
@@ -152,6 +160,7 @@ bool getenv_flag_direct_store();
 int forced_tile_n();
 int stream_overlap_mode();  // int4_linear_set_overlap: 0 off, 1 weights stationary, 2 weights and X
 int two_pass_mode();  // -1 automatic, 0 never, 1 whenever the tensor-memory family is used
+int fewrows_mode();  // int4_linear_set_fewrows: -1 by shape, 0 never, 1 whenever the kernel can run
 int tail_mode();  // int4_linear_set_tail: -1 automatic, 0 whole tiles only, 1 half-width items, 2 cut along K
 int forced_pairs();  // -1 automatic, 0 never use CTA pairs, 1 always (m > 128)
 

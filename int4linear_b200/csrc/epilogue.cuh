@@ -89,6 +89,71 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
     }
 }
 
+// Swapped operands (gemm_fewrows.cu): the accumulator is a tile of Y transposed -- lane = row of W =
+// column of Y, accumulator column = row of X = row of Y.  w_rows and x_rows are Y's column and row
+// counts.  The warp writes its 32 x 32 block transposed into a 128-byte-swizzled staging tile (for each
+// accumulator column the 32 lanes fill one 128-byte row: no bank conflicts) and one bulk store -- or
+// bulk reduction, for a share of a tile that is cut along K -- moves it into Y, clipping the tails.
+// Needs a 16-byte row pitch of Y (columns % 4 == 0).
+template <bool kAdd>
+__device__ __forceinline__ void drain_accumulator_transposed_tma(uint32_t t_addr, int width, int row0, int col0, int w_rows, int x_rows,
+                                                                 const int* __restrict__ bias, const CUtensorMap* tm_y,
+                                                                 uint32_t stg, int lane)
+{
+    const int ycol = row0 + lane;
+    const int b = (bias != nullptr && ycol < w_rows) ? __ldg(bias + ycol) : 0;
+    if (row0 >= w_rows) return;
+#pragma unroll 1
+    for (int c = 0; c < width; c += 32) {
+        if (col0 + c >= x_rows) break;
+        uint32_t v[32];
+        tmem_ld_32x32(t_addr + c, v);
+        tmem_ld_wait();
+        // The store issued for the previous block read this tile; make sure it is done.
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            sts32(stg + i * 128 + ((((lane >> 2) ^ (i & 7))) << 4) + (lane & 3) * 4,
+                  static_cast<uint32_t>((static_cast<int>(v[i]) >> 8) + b));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            if constexpr (kAdd) tma_reduce_add_2d(tm_y, stg, row0, col0 + c);
+            else tma_store_2d(tm_y, stg, row0, col0 + c);
+            tma_store_commit();
+        }
+    }
+}
+
+// The same with per-thread stores, for any row pitch of Y: for each accumulator column the warp
+// writes 32 neighbouring int32 of one row of Y (one 128-byte request), or adds them atomically.
+template <bool kAdd>
+__device__ __forceinline__ void drain_accumulator_transposed(uint32_t t_addr, int width, int row0, int col0, int w_rows, int x_rows,
+                                                             int* __restrict__ y, const int* __restrict__ bias, int lane)
+{
+    const int ycol = row0 + lane;
+    const bool col_ok = ycol < w_rows;
+    const int b = (bias != nullptr && col_ok) ? __ldg(bias + ycol) : 0;
+#pragma unroll 1
+    for (int c = 0; c < width; c += 32) {
+        if (col0 + c >= x_rows) break;
+        uint32_t v[32];
+        tmem_ld_32x32(t_addr + c, v);
+        tmem_ld_wait();
+        if (!col_ok) continue;
+        int* dst = y + static_cast<size_t>(col0 + c) * w_rows + ycol;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (col0 + c + i < x_rows) {
+                const int val = (static_cast<int>(v[i]) >> 8) + b;
+                if constexpr (kAdd) atomicAdd(dst + static_cast<size_t>(i) * w_rows, val);
+                else dst[static_cast<size_t>(i) * w_rows] = val;
+            }
+        }
+    }
+}
+
 // Dequantising variant: float(acc) * row_scale[row] * col_scale[col] + bias[col], rounded to
 // bfloat16 or half (round to nearest even), written with per-thread 16-byte stores (8 values) where the
 // row pitch allows.  The int32 -> float conversion is exact (|acc| <= 64 K < 2^24).

@@ -80,6 +80,13 @@ struct Cfg {
     static constexpr int kSmemBytes = 1024 /*alignment slack*/ + U * kUpStage + P * kPkStage +
                                       kStoreStageBytes + kNumBarriers * 8 + 16;
     static_assert(P >= kGroups && U >= kGroups, "every unpack group needs a slot of its own");
+    // Every use of a packed slot must be consumed by the same unpack group.  A wait names a phase by
+    // its parity only, and TMA loads do not land in the order they were issued: a group that runs
+    // ahead could otherwise ask for a slot's next use while the use before it -- the other group's --
+    // is still in flight, find the parity it wants (left by the use before that) and read a slot
+    // that has not arrived.  The same holds for the slots TMA fills with expanded weights.  (Slots
+    // released by tcgen05.commit complete in issue order; for those U >= kGroups is enough.)
+    static_assert(P % kGroups == 0 && (!PREW || U % kGroups == 0), "a TMA-filled slot must stay with one unpack group");
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns: power of two");
     static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
@@ -255,7 +262,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
             tile_coord(sched, sg.tile, &tm, &tn);
             const int col_off = sg.col_off, width = sg.width;
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
-            if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
+            if (!mbar_wait_warp(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN + col_off;
@@ -309,7 +316,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
-                if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
+                if (!mbar_wait_warp(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
                 const uint32_t src = pk_base + ps * C::kPkStage;
                 const uint32_t dst = up_base + us * C::kUpStage;
                 // All loads first, so their latencies overlap.
@@ -317,7 +324,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
 #pragma unroll
                 for (int i = 0; i < kPerThread; ++i)
                     if (i * kGroupThreads + gtid < chunks) x[i] = lds128(src + (i * kGroupThreads + gtid) * 16);
-                if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                if (!mbar_wait_warp(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
 #pragma unroll
                 for (int i = 0; i < kPerThread; ++i) {
                     const int q = i * kGroupThreads + gtid;
@@ -336,7 +343,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 fence_proxy_async_smem();
                 if constexpr (C::kPreW) {
                     // The slot is complete only when TMA has also delivered its expanded W rows.
-                    if (!mbar_wait(w_full(us), ur & 1u, abort_flag)) { alive = false; break; }
+                    if (!mbar_wait_warp(w_full(us), ur & 1u, abort_flag)) { alive = false; break; }
                 }
                 __syncwarp();
                 if (lane == 0) {
@@ -398,8 +405,9 @@ gemm_s4_tcgen05_gather_kernel(const __grid_constant__ CUtensorMap tm_x,
 
 // Clears the tiles the next GEMM launch cuts along K (its shares only add into them).  One block per
 // tile, whole 16-byte stores where the row pitch allows; rows and columns beyond Y are skipped.
+// transposed: the tiles are tiles of Y transposed (gemm_fewrows.cu); m and n stay Y's own rows and columns.
 __global__ void __launch_bounds__(256)
-clear_cut_tiles_kernel(int* __restrict__ y, int m, int n, const Schedule sched, int tile_m, int bn)
+clear_cut_tiles_kernel(int* __restrict__ y, int m, int n, const Schedule sched, int tile_m, int bn, bool transposed)
 {
     // The GEMM behind this kernel is launched with programmatic stream serialisation: it may start
     // right away and run its main loops while the tiles are being cleared; its epilogue warps wait
@@ -407,8 +415,8 @@ clear_cut_tiles_kernel(int* __restrict__ y, int m, int n, const Schedule sched, 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     int tm, tn;
     tile_coord(sched, sched.whole + static_cast<int>(blockIdx.x), &tm, &tn);
-    const int row0 = tm * tile_m, col0 = tn * bn;
-    const int rows = min(tile_m, m - row0), cols = min(bn, n - col0);
+    const int row0 = transposed ? tn * bn : tm * tile_m, col0 = transposed ? tm * tile_m : tn * bn;
+    const int rows = min(transposed ? bn : tile_m, m - row0), cols = min(transposed ? tile_m : bn, n - col0);
     if (rows <= 0 || cols <= 0) return;
     const bool vec_ok = (n & 3) == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && (cols & 3) == 0;
     if (vec_ok) {
@@ -425,7 +433,18 @@ clear_cut_tiles_kernel(int* __restrict__ y, int m, int n, const Schedule sched, 
     }
 }
 
-using Cfg256 = Cfg<256, 3, 2, 1>;
+}  // namespace
+
+int launch_clear_cut_tiles(int* y, int m, int n, const Schedule& sched, int tile_m, int bn, bool transposed, cudaStream_t stream)
+{
+    clear_cut_tiles_kernel<<<sched.sk_tiles, 256, 0, stream>>>(y, m, n, sched, tile_m, bn, transposed);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
+}
+
+namespace {
+
+using Cfg256 = Cfg<256, 4, 2, 1>;
 using Cfg128 = Cfg<128, 4, 3, 1>;
 using Cfg64 = Cfg<64, 4, 4, 1>;
 using Cfg256x2 = Cfg<256, 4, 4, 2>;  // 256 x 256 tile on a CTA pair (a fourth expanded slot is worth 4 %)
@@ -477,9 +496,8 @@ int launch_cfg(DeviceCtx* ctx, const Problem& p, cudaStream_t stream, const Gath
     }
     if (sched.sk_tiles > 0) {
         // The cut tiles only receive additions: clear them first, on the same stream.
-        clear_cut_tiles_kernel<<<sched.sk_tiles, 256, 0, stream>>>(static_cast<int*>(p.y), p.m, p.n, sched, C::kTileM, C::kBN);
-        count_launch();
-        if (cudaGetLastError() != cudaSuccess) return INT4L_ERR_CUDA;
+        rc = launch_clear_cut_tiles(static_cast<int*>(p.y), p.m, p.n, sched, C::kTileM, C::kBN, false, stream);
+        if (rc != INT4L_OK) return rc;
     }
     const int workers = sched.workers;
     cudaLaunchConfig_t cfg = {};
@@ -585,6 +603,9 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
             return tma_store ? launch_cfg<Cfg256x2W, true>(ctx, p, stream) : launch_cfg<Cfg256x2W, false>(ctx, p, stream);
         return tma_store ? launch_cfg<Cfg128W, true>(ctx, p, stream) : launch_cfg<Cfg128W, false>(ctx, p, stream);
     }
+    // A few rows of X: operands swapped and W through tensor memory (gemm_fewrows.cu).
+    if (fewrows_supports(p) && (fewrows_mode() == 1 || (fewrows_mode() < 0 && forced_tile_n() == 0 && forced_pairs() < 0)))
+        return launch_fewrows(ctx, p, stream);
     // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
     // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile
     // re-expands X less often per output, a narrower one fills more SMs when the problem is small.

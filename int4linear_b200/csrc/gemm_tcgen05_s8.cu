@@ -173,7 +173,7 @@ gemm_s8_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x,
             int tm, tn;
             tile_coord(tile, tm, tn);
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
-            if (!mbar_wait(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
+            if (!mbar_wait_warp(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
             const int row0 = (tm * CTAS + static_cast<int>(cta_rank)) * kBM + sp * 32;
             const int col0 = tn * BN;

@@ -142,10 +142,13 @@ I4L_HD bool segment_of(const Schedule& s, int worker, int bn, int i, Segment* ou
 // `max_workers` workers.  can_add: partial sums may be added into the output (int32 Y of one GPU);
 // can_halve: half-width items are available; force_add: cut whenever it is possible, whatever the
 // estimate says (tests, experiments); block_time: time of this tile shape's K block relative to the
-// CTA pair's (the cut's overhead is a time, and counts for fewer of the longer K blocks).  *cost
-// receives the time of the busiest worker in tile times, for the dispatcher's choice between tile shapes.
+// CTA pair's (the cut's overhead is a time, and counts for fewer of the longer K blocks);
+// cut_overhead >= 0: the cut's overhead in K blocks of the calling kernel, measured for that kernel,
+// instead of the estimate for 256 x 256 pair tiles.  *cost receives the time of the busiest worker in
+// tile times, for the dispatcher's choice between tile shapes.
 inline Schedule plan_schedule(int tiles_m, int tiles_n, int kb_count, int max_workers, bool can_add, bool can_halve,
-                              double* cost = nullptr, bool force_add = false, double block_time = 1.0)
+                              double* cost = nullptr, bool force_add = false, double block_time = 1.0,
+                              double cut_overhead = -1.0)
 {
     Schedule s;
     s.tiles_m = tiles_m;
@@ -161,8 +164,9 @@ inline Schedule plan_schedule(int tiles_m, int tiles_n, int kb_count, int max_wo
         long long skw = units / kSkMinBlocks;
         if (skw > max_workers) skw = max_workers;
         const long long longest = skw > 0 ? (units + skw - 1) / skw : kb_count;
-        const double cut_cost = (static_cast<double>(longest) +
-                                 (kSkSplitCostBase + kSkSplitCostPerFullWave * rem / max_workers) / block_time) / kb_count;
+        const double overhead = cut_overhead >= 0.0 ? cut_overhead
+                                                    : (kSkSplitCostBase + kSkSplitCostPerFullWave * rem / max_workers) / block_time;
+        const double cut_cost = (static_cast<double>(longest) + overhead) / kb_count;
         // A half-width item still expands the whole X tile: about 0.75 of a tile time; a launch that
         // consists of nothing else is dominated by filling the pipeline (measured).
         const bool halvable = can_halve && 2 * rem <= max_workers;

@@ -300,6 +300,13 @@ def set_two_pass(mode: int) -> int:
     return st
 
 
+def set_fewrows(mode: int) -> None:
+    """-1 by shape, 0 never, 1 whenever M <= 64: the few-rows kernel with W in tensor memory (int4_linear_set_fewrows)."""
+    st = _lib.load().int4_linear_set_fewrows(mode)
+    if st != 0:
+        raise Int4LinearError(st, "int4_linear_set_fewrows")
+
+
 def set_tail(mode: int) -> None:
     """-1 automatic, 0 whole tiles, 1 half-width items, 2 last wave cut along K (int4_linear_set_tail)."""
     st = _lib.load().int4_linear_set_tail(mode)

@@ -80,6 +80,7 @@ def test_tail_shapes(cuda, shape, vname, variant):
 def test_skinny_kernel(cuda, shape):
     m, n, k = shape
     x, w, xp, wp = make_case(m, n, k, seed=9)
+    # up to 32 rows the register kernels (from 17 rows on only while the weights are small)
     assert L.path_for(m, n, k) == (L.PATH_SKINNY if m <= 32 else L.PATH_TCGEN05)
     y = run_device(cuda, xp, wp, k, path=L.PATH_SKINNY)
     ref = O.linear_ref_sgemm(x, w) if m * n * k > 2e8 else O.linear_ref(x.astype(np.int32), w.astype(np.int32))
