@@ -228,7 +228,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % kP, pr = it / kP;
                 const uint32_t us = it % kU, ur = it / kU;
-                if (!mbar_wait_warp(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
+                if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
                 const uint32_t src = pk_base + ps * kPkStage;
                 uint4 wq[8], xq[4];
 #pragma unroll

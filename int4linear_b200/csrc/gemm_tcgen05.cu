@@ -316,7 +316,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 if (static_cast<int>(it % kGroups) != group) continue;
                 const uint32_t ps = it % P, pr = it / P;
                 const uint32_t us = it % U, ur = it / U;
-                if (!mbar_wait_warp(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
+                if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
                 const uint32_t src = pk_base + ps * C::kPkStage;
                 const uint32_t dst = up_base + us * C::kUpStage;
                 // All loads first, so their latencies overlap.
@@ -324,7 +324,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
 #pragma unroll
                 for (int i = 0; i < kPerThread; ++i)
                     if (i * kGroupThreads + gtid < chunks) x[i] = lds128(src + (i * kGroupThreads + gtid) * 16);
-                if (!mbar_wait_warp(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                if (!mbar_wait(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
 #pragma unroll
                 for (int i = 0; i < kPerThread; ++i) {
                     const int q = i * kGroupThreads + gtid;
@@ -343,7 +343,7 @@ gemm_s4_tcgen05_body(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUt
                 fence_proxy_async_smem();
                 if constexpr (C::kPreW) {
                     // The slot is complete only when TMA has also delivered its expanded W rows.
-                    if (!mbar_wait_warp(w_full(us), ur & 1u, abort_flag)) { alive = false; break; }
+                    if (!mbar_wait(w_full(us), ur & 1u, abort_flag)) { alive = false; break; }
                 }
                 __syncwarp();
                 if (lane == 0) {
