@@ -89,6 +89,17 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
     }
 }
 
+// The few-rows kernel spreads its UMMAs over two issuing threads with an accumulator each (second_acc:
+// the other accumulator's distance in columns, or -1 when only one of them holds anything).
+__device__ __forceinline__ void add_second_accumulator(uint32_t t_addr, uint32_t (&v)[32])
+{
+    uint32_t u[32];
+    tmem_ld_32x32(t_addr, u);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += u[i];
+}
+
 // Swapped operands (gemm_fewrows.cu): the accumulator is a tile of Y transposed -- lane = row of W =
 // column of Y, accumulator column = row of X = row of Y.  w_rows and x_rows are Y's column and row
 // counts.  The warp writes its 32 x 32 block transposed into a 128-byte-swizzled staging tile (for each
@@ -98,7 +109,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, int width, in
 template <bool kAdd>
 __device__ __forceinline__ void drain_accumulator_transposed_tma(uint32_t t_addr, int width, int row0, int col0, int w_rows, int x_rows,
                                                                  const int* __restrict__ bias, const CUtensorMap* tm_y,
-                                                                 uint32_t stg, int lane)
+                                                                 uint32_t stg, int lane, int second_acc = -1)
 {
     const int ycol = row0 + lane;
     const int b = (bias != nullptr && ycol < w_rows) ? __ldg(bias + ycol) : 0;
@@ -109,6 +120,7 @@ __device__ __forceinline__ void drain_accumulator_transposed_tma(uint32_t t_addr
         uint32_t v[32];
         tmem_ld_32x32(t_addr + c, v);
         tmem_ld_wait();
+        if (second_acc >= 0) add_second_accumulator(t_addr + second_acc + c, v);
         // The store issued for the previous block read this tile; make sure it is done.
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
@@ -130,7 +142,8 @@ __device__ __forceinline__ void drain_accumulator_transposed_tma(uint32_t t_addr
 // writes 32 neighbouring int32 of one row of Y (one 128-byte request), or adds them atomically.
 template <bool kAdd>
 __device__ __forceinline__ void drain_accumulator_transposed(uint32_t t_addr, int width, int row0, int col0, int w_rows, int x_rows,
-                                                             int* __restrict__ y, const int* __restrict__ bias, int lane)
+                                                             int* __restrict__ y, const int* __restrict__ bias, int lane,
+                                                             int second_acc = -1)
 {
     const int ycol = row0 + lane;
     const bool col_ok = ycol < w_rows;
@@ -141,6 +154,7 @@ __device__ __forceinline__ void drain_accumulator_transposed(uint32_t t_addr, in
         uint32_t v[32];
         tmem_ld_32x32(t_addr + c, v);
         tmem_ld_wait();
+        if (second_acc >= 0) add_second_accumulator(t_addr + second_acc + c, v);
         if (!col_ok) continue;
         int* dst = y + static_cast<size_t>(col0 + c) * w_rows + ycol;
 #pragma unroll

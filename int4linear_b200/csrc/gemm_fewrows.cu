@@ -22,7 +22,8 @@
 //     CTA needs bandwidth x latency bytes in flight.
 // Replaces, for these shapes, kernels/linear_v21.h:471-753 run on a 256 x 128 tile of padding.
 //
-// Tensor memory (512 columns): two accumulator buffers of 64 columns, then kU stages of 64 columns
+// Tensor memory (512 columns): two accumulator buffers of two accumulators (one per issuing thread)
+// of 64 columns, then kU stages of 64 columns
 // for W (lane = W row; 32-bit column c of a stage holds bytes 4c .. 4c+3 of the expanded row; UMMA j of
 // a K step reads columns 8j .. 8j+7).  The expanded row is [even elements of packed chunk j | odd
 // elements of packed chunk j] for j = 0 .. 7 -- the order the X rows have in shared memory, so both
@@ -61,7 +62,8 @@ constexpr int kUpStage = 2 * kXTile;
 constexpr int kAccCols = kMaxRowsX;
 constexpr int kStageCols = kBKBytes / 2;           // tensor-memory columns of one expanded W stage
 constexpr int kTmemCols = 512;
-constexpr int kTmemWCol = 2 * kAccCols;  // first column of the W stages
+constexpr int kIssuers = 2;                          // threads that issue UMMAs (alternate K steps), an accumulator each
+constexpr int kTmemWCol = 2 * kIssuers * kAccCols;  // first column of the W stages
 constexpr int kNumBarriers = 2 * kP + 2 * kU + 4;
 constexpr int kStoreStageBytes = 4 * 4096;          // one 32 x 32 int32 staging tile per epilogue warp
 constexpr int kSmemBytes = 1024 + kU * kUpStage + kP * kPkStage + kStoreStageBytes + kNumBarriers * 8 + 16;
@@ -69,14 +71,14 @@ static_assert(kTmemWCol + kStageCols * kU <= kTmemCols, "tensor memory budget");
 static_assert(kUpStage % 1024 == 0 && kPkStage % 1024 == 0, "stage bases must keep the swizzle alignment");
 static_assert(kSmemBytes <= 232448, "shared memory budget");
 
-__global__ void __launch_bounds__(32 * (6 + 4 * kGroups), 1)
+__global__ void __launch_bounds__(32 * (7 + 4 * kGroups), 1)
 gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                        const __grid_constant__ CUtensorMap tm_x,
                        const __grid_constant__ CUtensorMap tm_y, int tma_store,
                        int* __restrict__ y, int w_rows, int x_rows, int x_pad,
                        const Schedule sched, int* status, const int* __restrict__ bias)
 {
-    constexpr int kThreads = 32 * (6 + 4 * kGroups);
+    constexpr int kThreads = 32 * (7 + 4 * kGroups);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -104,6 +106,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
             // pk_full | pk_empty | up_full | up_empty | tm_full | tm_empty
             uint32_t count = 1;
             if (b >= kP && b < 2 * kP + kU) count = 4;                 // the four warps of a group
+            else if (b >= 2 * kP + 2 * kU && b < 2 * kP + 2 * kU + 2) count = kIssuers;  // every issuer commits
             else if (b >= 2 * kP + 2 * kU + 2) count = 4;              // the four epilogue warps
             mbar_init(bar_base + 8u * b, count);
         }
@@ -149,8 +152,15 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------- UMMA issuer
+    } else if (warp == 1 || warp == 6 + 4 * kGroups) {
+        // ------------------------------------------------------ UMMA issuers
+        // Issuing one tcgen05.mma with its A operand in tensor memory keeps the issuing thread busy
+        // for about a hundred cycles whatever N is, and a commit for two hundred (measured: 440 ns for
+        // the eight UMMAs of a step, 540 with the commit), while the tensor pipe needs 32 cycles per
+        // UMMA at N = 64.  Two threads in different warps therefore take alternate K steps, each into
+        // an accumulator of its own (UMMAs of different threads are not ordered against one another);
+        // the epilogue adds the two.
+        const uint32_t which = warp == 1 ? 0u : 1u;
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_s8(kRowsW, x_pad);
             uint32_t it = 0, local_tile = 0;
@@ -160,8 +170,10 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                 const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
                 if (!mbar_wait(tm_empty(buf), (br & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * kAccCols;
+                const uint32_t d_tmem = tmem_base + (buf * kIssuers + which) * kAccCols;
+                bool first = true;
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                    if ((it & 1u) != which) continue;
                     const uint32_t s = it % kU, r = it / kU;
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
                     tc_fence_after_sync();
@@ -170,18 +182,19 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                     for (int j = 0; j < 8; ++j) {
                         // 32 bytes of K per instruction: 8 columns of tensor memory, 32 bytes of an X row
                         const uint64_t b_desc = umma_desc_sw128(up_base + s * kUpStage + (j >> 2) * kXTile) + 2u * (j & 3);
-                        umma_i8_a_tmem(d_tmem, a_tmem + 8u * j, b_desc, idesc, (kb != sg.kb0 || j != 0) ? 1u : 0u);
+                        umma_i8_a_tmem(d_tmem, a_tmem + 8u * j, b_desc, idesc, (first && j == 0) ? 0u : 1u);
                     }
+                    first = false;
                     umma_commit(up_empty(s));
                 }
-                if (alive) umma_commit(tm_full(buf));
+                if (alive) umma_commit(tm_full(buf));  // with nothing issued in this segment it arrives at once
             }
         }
         __syncwarp();
     } else if (warp < 6) {
         // ---------------------------------------------------------- epilogue
         const int sp = warp & 3;  // quarter of the tensor-memory lanes this warp may read
-        uint32_t local_tile = 0;
+        uint32_t local_tile = 0, it = 0;
         bool alive = true;
         Segment sg;
         // Behind a clearing kernel this grid starts early; nothing is added into Y before that
@@ -194,18 +207,23 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (!mbar_wait_warp(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
             const int row0 = tm * kRowsW + sp * 32;
-            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + buf * kAccCols;
+            // Which issuers hold a part of this segment: both unless it is a single step.
+            const uint32_t steps = static_cast<uint32_t>(sg.kb1 - sg.kb0);
+            const uint32_t first_acc = steps >= 2 ? 0u : (it & 1u);
+            const int second_acc = steps >= 2 ? kAccCols : -1;
+            it += steps;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + (buf * kIssuers + first_acc) * kAccCols;
             const int width = (x_pad + 31) & ~31;  // whole 32-column loads; columns beyond x_rows are not written
             if (tma_store) {
                 const uint32_t stg = st_base + (warp - 2) * 4096;
                 if (sg.mode != kSegStore)
-                    drain_accumulator_transposed_tma<true>(t_addr, width, row0, 0, w_rows, x_rows, sg.mode == kSegAddFirst ? bias : nullptr, &tm_y, stg, lane);
+                    drain_accumulator_transposed_tma<true>(t_addr, width, row0, 0, w_rows, x_rows, sg.mode == kSegAddFirst ? bias : nullptr, &tm_y, stg, lane, second_acc);
                 else
-                    drain_accumulator_transposed_tma<false>(t_addr, width, row0, 0, w_rows, x_rows, bias, &tm_y, stg, lane);
+                    drain_accumulator_transposed_tma<false>(t_addr, width, row0, 0, w_rows, x_rows, bias, &tm_y, stg, lane, second_acc);
             } else if (sg.mode != kSegStore) {
-                drain_accumulator_transposed<true>(t_addr, width, row0, 0, w_rows, x_rows, y, sg.mode == kSegAddFirst ? bias : nullptr, lane);
+                drain_accumulator_transposed<true>(t_addr, width, row0, 0, w_rows, x_rows, y, sg.mode == kSegAddFirst ? bias : nullptr, lane, second_acc);
             } else {
-                drain_accumulator_transposed<false>(t_addr, width, row0, 0, w_rows, x_rows, y, bias, lane);
+                drain_accumulator_transposed<false>(t_addr, width, row0, 0, w_rows, x_rows, y, bias, lane, second_acc);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -214,7 +232,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
         if (tma_store && lane == 0) tma_store_wait_all<0>();
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ unpack
+        // ------------------------------------------------------------ unpack (warps 6 .. 6 + 4 * kGroups - 1)
         const int uw = warp - 6;
         const int group = uw >> 2;
         const int sp = warp & 3;             // the lanes of tensor memory this warp may write
@@ -330,7 +348,7 @@ int launch_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sched.workers, 1, 1);
-    cfg.blockDim = dim3(32 * (6 + 4 * kGroups), 1, 1);
+    cfg.blockDim = dim3(32 * (7 + 4 * kGroups), 1, 1);
     cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
