@@ -1,7 +1,7 @@
-// GEMM kernel for a few rows of X (M <= 64): the operands change places and W goes through tensor
+// GEMM kernel for a few rows of X (M <= 128): the operands change places and W goes through tensor
 // memory instead of shared memory.
 //
-// With M <= 64 every byte of W is used once, so the operator is a stream of W from HBM, and in the
+// With so few rows every byte of W is used once, so the operator is a stream of W from HBM, and in the
 // main kernel (gemm_tcgen05.cu) such a stream is held back twice: by the rate at which one SM's TMA
 // unit turns out requests (a box of 64-byte rows is one request per row, and with only those loads
 // left in the kernel a CTA still needs a quarter of a microsecond per 8 KB of W), and by the
@@ -17,13 +17,18 @@
 //     16-byte reads are conflict-free), expand them in registers and write the 256 bytes straight
 //     into tensor memory (tcgen05.st); the UMMA takes its A operand from there.  W costs shared
 //     memory its packed bytes only, written once and read once;
-//   * X (at most 64 rows) is expanded into shared memory per K step as in the main kernel;
-//   * the ring of packed stages holds 6 x 16 KB of W, because with every byte coming from HBM once a
-//     CTA needs bandwidth x latency bytes in flight.
+//   * X is expanded into shared memory per K step as in the main kernel;
+//   * the ring of packed stages holds 6 x 16 KB of W (4 x 16 KB in the two-half form), because with
+//     every byte coming from HBM once a CTA needs bandwidth x latency bytes in flight.
+// Two forms (template parameter XH, the number of 64-row halves of X).  XH = 1, M <= 64: the two
+// UMMA-issuing threads take alternate K steps, each into an accumulator of its own, and the epilogue
+// adds the two.  XH = 2, 65 <= M <= 128: every stage of W in tensor memory is multiplied with both
+// halves of X, issuing thread h taking half h in every step, so W is still loaded and expanded once
+// and accumulator h is rows 64h .. of Y.
 // Replaces, for these shapes, kernels/linear_v21.h:471-753 run on a 256 x 128 tile of padding.
 //
 // Tensor memory (512 columns): two accumulator buffers of two accumulators (one per issuing thread)
-// of 64 columns, then kU stages of 64 columns
+// of 64 columns, then the stages of 64 columns
 // for W (lane = W row; 32-bit column c of a stage holds bytes 4c .. 4c+3 of the expanded row; UMMA j of
 // a K step reads columns 8j .. 8j+7).  The expanded row is [even elements of packed chunk j | odd
 // elements of packed chunk j] for j = 0 .. 7 -- the order the X rows have in shared memory, so both
@@ -42,43 +47,52 @@ namespace i4l {
 namespace {
 
 constexpr int kRowsW = 128;        // W rows per tile = UMMA M = lanes of tensor memory
-constexpr int kMaxRowsX = 64;      // X rows (UMMA N) at most
+constexpr int kHalfRowsX = 64;     // X rows per UMMA (its N) at most
 constexpr int kBKBytes = 128;      // packed bytes per row per K step (256 elements)
 constexpr int kGroups = 2;         // groups of four unpack warps; group g converts K steps g, g + kGroups, ...
-constexpr int kP = 6;              // packed stages
-constexpr int kU = 4;              // expanded stages: W in tensor memory, X in shared memory
-// Every use of a packed stage must be consumed by the same unpack group.  A wait names a phase by
-// its parity only, and TMA loads do not land in the order they were issued: a group that runs ahead
-// could otherwise ask for a stage's next use while the use before it -- the other group's -- is still
-// in flight, find the parity it wants (left by the use before that) and read a stage that has not
-// arrived.  (The expanded stages are released by tcgen05.commit in issue order, so for them it is
-// enough that the ring is at least as deep as there are groups.)
-static_assert(kP % kGroups == 0 && kU >= kGroups, "ring depths and unpack groups");
-// Measured with three groups: slower (14.0 against 13.7 us at 64 x 14336 x 4096); only two are tested.
-static_assert(kGroups == 2, "tested with two unpack groups");
-constexpr int kPkStage = (kRowsW + kMaxRowsX) * kBKBytes;
-constexpr int kXTile = kMaxRowsX * 128;            // expanded X of one 128-element half of a K step
-constexpr int kUpStage = 2 * kXTile;
-constexpr int kAccCols = kMaxRowsX;
+constexpr int kIssuers = 2;        // threads that issue UMMAs, an accumulator each
+constexpr int kXTile = kHalfRowsX * 128;           // expanded X: one 64-row half, one 128-element half of a K step
+constexpr int kAccCols = kHalfRowsX;
 constexpr int kStageCols = kBKBytes / 2;           // tensor-memory columns of one expanded W stage
 constexpr int kTmemCols = 512;
-constexpr int kIssuers = 2;                          // threads that issue UMMAs (alternate K steps), an accumulator each
 constexpr int kTmemWCol = 2 * kIssuers * kAccCols;  // first column of the W stages
-constexpr int kNumBarriers = 2 * kP + 2 * kU + 4;
 constexpr int kStoreStageBytes = 4 * 4096;          // one 32 x 32 int32 staging tile per epilogue warp
-constexpr int kSmemBytes = 1024 + kU * kUpStage + kP * kPkStage + kStoreStageBytes + kNumBarriers * 8 + 16;
-static_assert(kTmemWCol + kStageCols * kU <= kTmemCols, "tensor memory budget");
-static_assert(kUpStage % 1024 == 0 && kPkStage % 1024 == 0, "stage bases must keep the swizzle alignment");
-static_assert(kSmemBytes <= 232448, "shared memory budget");
+constexpr int kThreads = 32 * (7 + 4 * kGroups);
+// Measured with three groups: slower (14.0 against 13.7 us at 64 x 14336 x 4096); only two are tested.
+static_assert(kGroups == 2, "tested with two unpack groups");
 
-__global__ void __launch_bounds__(32 * (7 + 4 * kGroups), 1)
+// Ring geometry for XH halves of X.
+template <int XH>
+struct Geo {
+    static constexpr int kP = XH == 1 ? 6 : 4;       // packed stages
+    static constexpr int kU = XH == 1 ? 4 : 2;       // expanded stages: W in tensor memory, X in shared memory
+    static constexpr int kRowsX = XH * kHalfRowsX;
+    static constexpr int kPkStage = (kRowsW + kRowsX) * kBKBytes;
+    static constexpr int kUpStage = XH * 2 * kXTile;  // [half of X][half of the K step][64 rows x 128 B]
+    static constexpr int kNumBarriers = 2 * kP + 2 * kU + 4;
+    static constexpr int kSmemBytes = 1024 + kU * kUpStage + kP * kPkStage + kStoreStageBytes + kNumBarriers * 8 + 16;
+    // Every use of a packed stage must be consumed by the same unpack group.  A wait names a phase
+    // by its parity only, and TMA loads do not land in the order they were issued: a group that runs
+    // ahead could otherwise ask for a stage's next use while the use before it -- the other group's
+    // -- is still in flight, find the parity it wants (left by the use before that) and read a stage
+    // that has not arrived.  (The expanded stages are released by tcgen05.commit in issue order, so
+    // for them it is enough that the ring is at least as deep as there are groups.)
+    static_assert(kP % kGroups == 0 && kU >= kGroups, "ring depths and unpack groups");
+    static_assert(kTmemWCol + kStageCols * kU <= kTmemCols, "tensor memory budget");
+    static_assert(kUpStage % 1024 == 0 && kPkStage % 1024 == 0, "stage bases must keep the swizzle alignment");
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
+};
+
+template <int XH>
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                        const __grid_constant__ CUtensorMap tm_x,
                        const __grid_constant__ CUtensorMap tm_y, int tma_store,
                        int* __restrict__ y, int w_rows, int x_rows, int x_pad,
                        const Schedule sched, int* status, const int* __restrict__ bias)
 {
-    constexpr int kThreads = 32 * (7 + 4 * kGroups);
+    using G = Geo<XH>;
+    constexpr int kP = G::kP, kU = G::kU, kPkStage = G::kPkStage, kUpStage = G::kUpStage, kNumBarriers = G::kNumBarriers;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -106,6 +120,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
             // pk_full | pk_empty | up_full | up_empty | tm_full | tm_empty
             uint32_t count = 1;
             if (b >= kP && b < 2 * kP + kU) count = 4;                 // the four warps of a group
+            else if (b >= 2 * kP + kU && b < 2 * kP + 2 * kU) count = XH;  // the issuer(s) that read the stage
             else if (b >= 2 * kP + 2 * kU && b < 2 * kP + 2 * kU + 2) count = kIssuers;  // every issuer commits
             else if (b >= 2 * kP + 2 * kU + 2) count = 4;              // the four epilogue warps
             mbar_init(bar_base + 8u * b, count);
@@ -157,12 +172,12 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
         // Issuing one tcgen05.mma with its A operand in tensor memory keeps the issuing thread busy
         // for about a hundred cycles whatever N is, and a commit for two hundred (measured: 440 ns for
         // the eight UMMAs of a step, 540 with the commit), while the tensor pipe needs 32 cycles per
-        // UMMA at N = 64.  Two threads in different warps therefore take alternate K steps, each into
-        // an accumulator of its own (UMMAs of different threads are not ordered against one another);
-        // the epilogue adds the two.
+        // UMMA at N = 64.  Two threads in different warps therefore share the work, each with an
+        // accumulator of its own (UMMAs of different threads are not ordered against one another):
+        // alternate K steps, the epilogue adding the two (XH = 1), or one half of X each (XH = 2).
         const uint32_t which = warp == 1 ? 0u : 1u;
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_s8(kRowsW, x_pad);
+            const uint32_t idesc = umma_idesc_s8(kRowsW, XH == 1 ? x_pad : (which == 0 ? kHalfRowsX : x_pad - kHalfRowsX));
             uint32_t it = 0, local_tile = 0;
             bool alive = true;
             Segment sg;
@@ -173,7 +188,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                 const uint32_t d_tmem = tmem_base + (buf * kIssuers + which) * kAccCols;
                 bool first = true;
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
-                    if ((it & 1u) != which) continue;
+                    if (XH == 1 && (it & 1u) != which) continue;
                     const uint32_t s = it % kU, r = it / kU;
                     if (!mbar_wait(up_full(s), r & 1u, abort_flag)) { alive = false; break; }
                     tc_fence_after_sync();
@@ -181,7 +196,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         // 32 bytes of K per instruction: 8 columns of tensor memory, 32 bytes of an X row
-                        const uint64_t b_desc = umma_desc_sw128(up_base + s * kUpStage + (j >> 2) * kXTile) + 2u * (j & 3);
+                        const uint64_t b_desc = umma_desc_sw128(up_base + s * kUpStage + (XH == 2 ? which * 2 * kXTile : 0) + (j >> 2) * kXTile) + 2u * (j & 3);
                         umma_i8_a_tmem(d_tmem, a_tmem + 8u * j, b_desc, idesc, (first && j == 0) ? 0u : 1u);
                     }
                     first = false;
@@ -207,23 +222,30 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (!mbar_wait_warp(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
             const int row0 = tm * kRowsW + sp * 32;
-            // Which issuers hold a part of this segment: both unless it is a single step.
+            // XH = 1: which issuers hold a part of this segment (both unless it is a single step); their
+            // accumulators are added.  XH = 2: accumulator h is rows 64 h .. of Y.
             const uint32_t steps = static_cast<uint32_t>(sg.kb1 - sg.kb0);
-            const uint32_t first_acc = steps >= 2 ? 0u : (it & 1u);
-            const int second_acc = steps >= 2 ? kAccCols : -1;
+            const uint32_t first_acc = (XH == 2 || steps >= 2) ? 0u : (it & 1u);
+            const int second_acc = (XH == 1 && steps >= 2) ? kAccCols : -1;
             it += steps;
-            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + (buf * kIssuers + first_acc) * kAccCols;
-            const int width = (x_pad + 31) & ~31;  // whole 32-column loads; columns beyond x_rows are not written
-            if (tma_store) {
-                const uint32_t stg = st_base + (warp - 2) * 4096;
-                if (sg.mode != kSegStore)
-                    drain_accumulator_transposed_tma<true>(t_addr, width, row0, 0, w_rows, x_rows, sg.mode == kSegAddFirst ? bias : nullptr, &tm_y, stg, lane, second_acc);
-                else
-                    drain_accumulator_transposed_tma<false>(t_addr, width, row0, 0, w_rows, x_rows, bias, &tm_y, stg, lane, second_acc);
-            } else if (sg.mode != kSegStore) {
-                drain_accumulator_transposed<true>(t_addr, width, row0, 0, w_rows, x_rows, y, sg.mode == kSegAddFirst ? bias : nullptr, lane, second_acc);
-            } else {
-                drain_accumulator_transposed<false>(t_addr, width, row0, 0, w_rows, x_rows, y, bias, lane, second_acc);
+            const int* seg_bias = (sg.mode == kSegStore || sg.mode == kSegAddFirst) ? bias : nullptr;
+#pragma unroll
+            for (int h = 0; h < XH; ++h) {
+                const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + (buf * kIssuers + first_acc + h) * kAccCols;
+                const int col0 = h * kHalfRowsX;     // first row of Y (= row of X) of this accumulator
+                // whole 32-column loads; columns beyond x_rows are not written
+                const int width = XH == 1 ? ((x_pad + 31) & ~31) : (h == 0 ? kHalfRowsX : ((x_pad - kHalfRowsX + 31) & ~31));
+                if (tma_store) {
+                    const uint32_t stg = st_base + (warp - 2) * 4096;
+                    if (sg.mode != kSegStore)
+                        drain_accumulator_transposed_tma<true>(t_addr, width, row0, col0, w_rows, x_rows, seg_bias, &tm_y, stg, lane, second_acc);
+                    else
+                        drain_accumulator_transposed_tma<false>(t_addr, width, row0, col0, w_rows, x_rows, seg_bias, &tm_y, stg, lane, second_acc);
+                } else if (sg.mode != kSegStore) {
+                    drain_accumulator_transposed<true>(t_addr, width, row0, col0, w_rows, x_rows, y, seg_bias, lane, second_acc);
+                } else {
+                    drain_accumulator_transposed<false>(t_addr, width, row0, col0, w_rows, x_rows, y, seg_bias, lane, second_acc);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -239,7 +261,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
         const int wrow = sp * 32 + lane;     // this thread's W row of the tile
         const uint32_t wsw = wrow & 7;       // 128-byte swizzle of the packed W stage
         const int gtid = (uw & 3) * 32 + lane;
-        const int x_chunks = x_pad * 8;       // 16-byte packed chunks of the X stage (at most 512)
+        const int x_chunks = x_pad * 8;       // 16-byte packed chunks of the X stage (at most 512 per half of X)
         uint32_t it = 0;
         bool alive = true;
         Segment sg;
@@ -250,16 +272,24 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                 const uint32_t us = it % kU, ur = it / kU;
                 if (!mbar_wait(pk_full(ps), pr & 1u, abort_flag)) { alive = false; break; }
                 const uint32_t src = pk_base + ps * kPkStage;
-                uint4 wq[8], xq[4];
+                uint4 wq[8], xq[4 * XH];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) wq[c] = lds128(src + wrow * kBKBytes + ((c ^ wsw) << 4));
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4 * XH; ++i)
                     if (i * 128 + gtid < x_chunks) xq[i] = lds128(src + kRowsW * kBKBytes + (i * 128 + gtid) * 16);
-                // The packed stage is in registers now: hand it back to the producer at once (the
-                // arrive orders this thread's reads before it).
+                // Hand the packed stage back to the producer as soon as it is in registers -- which is
+                // when the loads have returned their data, not when they were issued: the arrive is
+                // made to depend on one destination register of every load (a warp's load instruction
+                // completes for all its lanes together, so lane 0's registers stand for the warp's).
+                uint32_t landed = 0;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) landed ^= wq[c].x;
+#pragma unroll
+                for (int i = 0; i < 4 * XH; ++i)
+                    if (i * 128 + gtid < x_chunks) landed ^= xq[i].x;
                 __syncwarp();
-                if (lane == 0) mbar_arrive(pk_empty(ps));
+                if (lane == 0) mbar_arrive_after(pk_empty(ps), landed);
                 if (!mbar_wait_warp(up_empty(us), (ur & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
@@ -277,11 +307,11 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
                     tmem_st_32x32(tmem_base + (static_cast<uint32_t>(sp * 32) << 16) + kTmemWCol + kStageCols * us + 32u * h, v);
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < 4 * XH; ++i) {
                     const int q = i * 128 + gtid;
                     if (q >= x_chunks) break;
-                    const int r = q >> 3, c = q & 3;
-                    const uint32_t dst = up_base + us * kUpStage + ((q >> 2) & 1) * kXTile;
+                    const int r = (q >> 3) & (kHalfRowsX - 1), c = q & 3;   // row within its half of X
+                    const uint32_t dst = up_base + us * kUpStage + (q >> 9) * 2 * kXTile + ((q >> 2) & 1) * kXTile;
                     uint4 lo, hi;
                     lo.x = (xq[i].x << 4) & 0xF0F0F0F0u; hi.x = xq[i].x & 0xF0F0F0F0u;
                     lo.y = (xq[i].y << 4) & 0xF0F0F0F0u; hi.y = xq[i].y & 0xF0F0F0F0u;
@@ -322,6 +352,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
 // clearing launch, a second epilogue per worker and the bulk reductions.
 constexpr double kCutOverheadSteps = 6.0;
 
+template <int XH>
 int launch_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
     const int x_pad = (p.m + 15) & ~15;
@@ -348,8 +379,8 @@ int launch_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sched.workers, 1, 1);
-    cfg.blockDim = dim3(32 * (7 + 4 * kGroups), 1, 1);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = Geo<XH>::kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     // Behind a clearing kernel: start while it runs (the epilogue waits for it, see the kernel).
@@ -357,7 +388,7 @@ int launch_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = sched.sk_tiles > 0 ? 1 : 0;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_s4_fewrows_kernel, tm_w, tm_x, tm_y, tma_store ? 1 : 0, static_cast<int*>(p.y), p.n, p.m, x_pad,
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_s4_fewrows_kernel<XH>, tm_w, tm_x, tm_y, tma_store ? 1 : 0, static_cast<int*>(p.y), p.n, p.m, x_pad,
                                              sched, ctx->status_dev, p.bias);
     count_launch();
     if (e != cudaSuccess) { cudaGetLastError(); return INT4L_ERR_CUDA; }
@@ -368,19 +399,21 @@ int launch_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 
 bool fewrows_supports(const Problem& p)
 {
-    return p.m <= kMaxRowsX && p.scaled.y16 == nullptr && !p.w_expanded;
+    return p.m <= 2 * kHalfRowsX && p.scaled.y16 == nullptr && !p.w_expanded;
 }
 
 int setup_fewrows(DeviceCtx*)
 {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_s4_fewrows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_s4_fewrows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<1>::kSmemBytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_s4_fewrows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<2>::kSmemBytes);
     return e == cudaSuccess ? INT4L_OK : INT4L_ERR_CUDA;
 }
 
 int launch_fewrows(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
 {
     if (!fewrows_supports(p)) return INT4L_ERR_UNSUPPORTED;
-    return launch_impl(ctx, p, stream);
+    return p.m <= kHalfRowsX ? launch_impl<1>(ctx, p, stream) : launch_impl<2>(ctx, p, stream);
 }
 
 }  // namespace i4l

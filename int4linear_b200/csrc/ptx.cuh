@@ -99,6 +99,22 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// Arrive, but not before the value `loaded` exists: for handing a buffer back right after LOADING
+// from it.  A load that has been issued has not yet read its data; the arrival's release does not
+// wait for it, and the buffer's next writer (TMA) could overwrite what the load is about to read.
+// Making the arrive instruction depend on a value computed from the loads' destination registers
+// holds it back until the data has arrived (either branch arrives; the predicate is the dependency).
+__device__ __forceinline__ void mbar_arrive_after(uint32_t bar, uint32_t loaded) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.eq.u32 p, %1, 0x5bd1e995;\n\t"
+        "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t"
+        "@!p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t"
+        "}\n" ::"r"(bar), "r"(loaded)
+        : "memory");
+}
+
 // Arrive on the barrier at the same shared-memory offset in CTA `cta` of this cluster.
 // Release semantics at CTA scope (the default), as for a local arrive: the data the
 // arrival publishes was written to shared memory through the generic proxy and fenced
