@@ -261,14 +261,15 @@ int int4_linear_set_tuning(int tile_n, int direct_store, int cta_pairs);
  * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_TAIL=none|half|kcut. */
 int int4_linear_set_tail(int mode);
 
-/* Few rows of X (M <= 64, int32 output): a kernel of its own (csrc/gemm_fewrows.cu) runs the
+/* Few rows of X (M <= 128, int32 output): a kernel of its own (csrc/gemm_fewrows.cu) runs the
  * tensor-memory GEMM with its operands swapped -- the 128-row side of each tile holds rows of W,
- * the narrow side (16 .. 64) the rows of X, the accumulator is a tile of Y transposed and the
- * epilogue writes it back transposed -- and passes W through tensor memory instead of shared
+ * the narrow side (16 .. 64, once or twice) the rows of X, the accumulator is a tile of Y transposed
+ * and the epilogue writes it back transposed -- and passes W through tensor memory instead of shared
  * memory, so that neither the tensor pipe nor the nibble expansion is spent on a 128-row X tile
- * that is mostly padding.  -1 (default): used for 17 <= M <= 64, and for M <= 16 where the decode
- * kernels cannot run; 0: never; 1: whenever M <= 64.  Results are identical either way.  The
- * reference runs every M on its one 256 x 128 tile (kernels/linear_v21.cu:12).
+ * that is mostly padding.  -1 (default): by shape -- 17 <= M <= 64 (from 17 to 32 only on large
+ * weights), 65 <= M <= 128 when N >= 4096, and M <= 16 where the decode kernels cannot run or K >
+ * 8192; 0: never; 1: whenever M <= 128.  Results are identical either way.  The reference runs
+ * every M on its one 256 x 128 tile (kernels/linear_v21.cu:12).
  * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_FEWROWS=0|1. */
 int int4_linear_set_fewrows(int mode);
 

@@ -603,8 +603,11 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
             return tma_store ? launch_cfg<Cfg256x2W, true>(ctx, p, stream) : launch_cfg<Cfg256x2W, false>(ctx, p, stream);
         return tma_store ? launch_cfg<Cfg128W, true>(ctx, p, stream) : launch_cfg<Cfg128W, false>(ctx, p, stream);
     }
-    // A few rows of X: operands swapped and W through tensor memory (gemm_fewrows.cu).
-    if (fewrows_supports(p) && (fewrows_mode() == 1 || (fewrows_mode() < 0 && forced_tile_n() == 0 && forced_pairs() < 0)))
+    // A few rows of X: operands swapped and W through tensor memory (gemm_fewrows.cu).  From 65 rows on
+    // only with at least 32 tiles of W rows: below that the 128 x 64 / 128 x 128 tiles of this kernel
+    // put more CTAs to work (128 x 1024 x 1024: 7.5 us here, 8.1 there; 128 x 6144 x 4096: 15.5 / 13.9).
+    if (fewrows_supports(p) && (fewrows_mode() == 1 || (fewrows_mode() < 0 && forced_tile_n() == 0 && forced_pairs() < 0 &&
+                                                          (p.m <= 64 || p.n >= 4096))))
         return launch_fewrows(ctx, p, stream);
     // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
     // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile

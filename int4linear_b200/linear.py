@@ -301,7 +301,7 @@ def set_two_pass(mode: int) -> int:
 
 
 def set_fewrows(mode: int) -> None:
-    """-1 by shape, 0 never, 1 whenever M <= 64: the few-rows kernel with W in tensor memory (int4_linear_set_fewrows)."""
+    """-1 by shape, 0 never, 1 whenever M <= 128: the few-rows kernel with W in tensor memory (int4_linear_set_fewrows)."""
     st = _lib.load().int4_linear_set_fewrows(mode)
     if st != 0:
         raise Int4LinearError(st, "int4_linear_set_fewrows")

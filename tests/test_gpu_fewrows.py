@@ -1,5 +1,5 @@
-"""GPU: the few-rows kernel (int4linear_b200/csrc/gemm_fewrows.cu; M <= 64, operands swapped, W
-through tensor memory, Y written back transposed).  Every shape is compared with the oracle, in the
+"""GPU: the few-rows kernel (int4linear_b200/csrc/gemm_fewrows.cu; M <= 128, operands swapped, W
+through tensor memory, Y written back transposed; one form for up to 64 rows, one for 65 to 128).  Every shape is compared with the oracle, in the
 kernel's three tail forms, with and without bias, through the bulk-store epilogue and the
 per-thread one (N % 4 != 0), with K tails, and against the main kernel on the same inputs.
 """
@@ -17,6 +17,9 @@ SHAPES = [
     (48, 4099, 1024), (57, 2050, 1056), (64, 1024, 8192), (64, 130, 288), (64, 14336, 1024),
     (24, 18944, 512),      # 148 tiles: exactly one per SM
     (64, 19200, 2048),     # 150 tiles: one whole wave, then two tiles cut along K
+    # 65 .. 128 rows: both halves of X against every stage of W
+    (65, 264, 1024), (80, 1000, 2048), (96, 4099, 1056), (100, 14336, 1024), (128, 129, 160), (128, 512, 256),
+    (111, 2050, 4096), (128, 19200, 1024), (72, 8, 32),
 ]
 
 
@@ -68,7 +71,7 @@ def test_fewrows_agrees_with_the_main_kernel_at_full_size(cuda, fewrows_on):
     """64 x 14336 x 4096 and 32 x 28672 x 8192: the few-rows kernel, whole tiles and cut, against the
     main kernel's 128-row tiles on the same device buffers (the oracle covers the smaller shapes)."""
     import torch
-    for (m, n, k) in [(64, 14336, 4096), (32, 28672, 8192), (17, 8192, 8192)]:
+    for (m, n, k) in [(64, 14336, 4096), (32, 28672, 8192), (17, 8192, 8192), (128, 14336, 4096), (96, 28672, 8192)]:
         g = torch.Generator(device=cuda)
         g.manual_seed(m + n)
         xd = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=cuda, generator=g)
@@ -97,6 +100,7 @@ def test_default_dispatch_by_shape(cuda):
     assert L.path_for(17, 14336, 4096) == L.PATH_TCGEN05
     assert L.path_for(33, 1024, 1024) == L.PATH_TCGEN05
     assert L.path_for(64, 4096, 4096) == L.PATH_TCGEN05
+    assert L.path_for(128, 4096, 4096) == L.PATH_TCGEN05
     m, n, k = 40, 1024, 2048
     x, w, xp, wp = make_case(m, n, k, seed=5)
     ref = O.linear_ref(x.astype(np.int32), w.astype(np.int32))
@@ -115,36 +119,37 @@ def test_default_dispatch_by_shape(cuda):
 
 def test_fewrows_in_replayed_graphs_and_on_several_streams(cuda, fewrows_on):
     """Back-to-back launches from a CUDA graph (every launch must leave the SMs' tensor memory and
-    barriers as it found them) and three streams at once, whole tiles and cut."""
+    barriers as it found them) and three streams at once, whole tiles and cut, both forms of the
+    kernel (48 and 112 rows; 74 tiles of 16 steps are cut into 148 shares in the automatic mode)."""
     import torch
-    m, n, k = 48, 9472, 4096   # 74 tiles of 16 steps: cut into 148 shares in the automatic mode
-    x, w, xp, wp = make_case(m, n, k, seed=77)
-    ref = torch.from_numpy(O.linear_ref_sgemm(x, w)).to(cuda)
-    xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
-    for mode in (-1, 0):
-        L.set_tail(mode)
-        ys = [torch.full((m, n), -1, dtype=torch.int32, device=cuda) for _ in range(4)]
-        L.linear(xd, wd, out=ys[0])
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(40):
-                    L.linear(xd, wd, out=ys[i % 4])
-        torch.cuda.current_stream().wait_stream(side)
-        for _ in range(25):
-            graph.replay()
-        torch.cuda.synchronize()
-        assert L.last_status() == 0
-        assert all(bool((y == ref).all()) for y in ys), f"graph, tail {mode}"
-        streams = [torch.cuda.Stream() for _ in range(3)]
-        outs = [torch.full((m, n), -1, dtype=torch.int32, device=cuda) for _ in range(3)]
-        for _ in range(10):
-            for s, y in zip(streams, outs):
-                with torch.cuda.stream(s):
-                    L.linear(xd, wd, out=y)
-        torch.cuda.synchronize()
-        assert L.last_status() == 0
-        assert all(bool((y == ref).all()) for y in outs), f"streams, tail {mode}"
+    for m, n, k in ((48, 9472, 4096), (112, 9472, 4096)):
+        x, w, xp, wp = make_case(m, n, k, seed=77)
+        ref = torch.from_numpy(O.linear_ref_sgemm(x, w)).to(cuda)
+        xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+        for mode in (-1, 0):
+            L.set_tail(mode)
+            ys = [torch.full((m, n), -1, dtype=torch.int32, device=cuda) for _ in range(4)]
+            L.linear(xd, wd, out=ys[0])
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(40):
+                        L.linear(xd, wd, out=ys[i % 4])
+            torch.cuda.current_stream().wait_stream(side)
+            for _ in range(25):
+                graph.replay()
+            torch.cuda.synchronize()
+            assert L.last_status() == 0
+            assert all(bool((y == ref).all()) for y in ys), f"graph, {m} rows, tail {mode}"
+            streams = [torch.cuda.Stream() for _ in range(3)]
+            outs = [torch.full((m, n), -1, dtype=torch.int32, device=cuda) for _ in range(3)]
+            for _ in range(10):
+                for s_, y in zip(streams, outs):
+                    with torch.cuda.stream(s_):
+                        L.linear(xd, wd, out=y)
+            torch.cuda.synchronize()
+            assert L.last_status() == 0
+            assert all(bool((y == ref).all()) for y in outs), f"streams, {m} rows, tail {mode}"
