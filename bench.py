@@ -19,8 +19,8 @@ test/benchmark.cu:112-113), default workload M=N=K=8192.
             resident operands, whichever is faster), or GB/s against the
             measured HBM copy rate for the decode shape
   configs   (1 GPU) a short event-timed figure for each of the five benchmark
-            configurations and for the decode shape with 32 and 64 rows, outside
-            `value`
+            configurations and for the decode shape with 32, 64 and 128 rows,
+            outside `value`
   cpu_baseline  the reference's own CPU GEMM on a bounded row sample
 
 With N > 1 ranks the weight matrix is sharded along N: every rank holds the
@@ -52,10 +52,11 @@ WORKLOADS = {
     "c4": (16, 14336, 4096, "hbm"),
     "c5": (8192, 28672, 8192, "tensor"),
     "m8": (8192, 8192, 8192, "tensor"),
-    # the decode shape c4 with a batch of 32 and of 64 rows (not BASELINE configurations: the shapes
-    # between the decode kernels and the 128-row tiles)
+    # the decode shape c4 with a batch of 32, 64 and 128 rows (not BASELINE configurations: the shapes
+    # between the decode kernels and full 128-row tiles)
     "d32": (32, 14336, 4096, "hbm"),
     "d64": (64, 14336, 4096, "hbm"),
+    "d128": (128, 14336, 4096, "hbm"),
 }
 NOMINAL_INT8_TOPS = 4500.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -885,7 +886,7 @@ def main():
         line["gather"] = gather_cmp
     if world == 1 and not args.no_configs:
         cfgs = {}
-        for name in ("c1", "c2", "c3", "c4", "c5", "d32", "d64"):
+        for name in ("c1", "c2", "c3", "c4", "c5", "d32", "d64", "d128"):
             try:
                 cfgs[name] = quick_config(torch, L, dev, flush, name, int8_peak, hbm_peak)
             except Exception as e:
