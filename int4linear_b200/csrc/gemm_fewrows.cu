@@ -348,9 +348,9 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
 }
 
 // What cutting the last wave along K costs this kernel, in its own K steps of 256 elements (measured:
-// 112 tiles of 16 steps on 148 SMs take 15.3 us cut against 13.8 us whole, at 0.5 us per step): the
-// clearing launch, a second epilogue per worker and the bulk reductions.
-constexpr double kCutOverheadSteps = 6.0;
+// 112 tiles of 16 steps on 148 SMs take 15.0 us cut, 13 steps per worker, against 12.9 us whole, at
+// 0.43 us per step): the clearing launch, a second epilogue per worker and the bulk reductions.
+constexpr double kCutOverheadSteps = 7.0;
 
 template <int XH>
 int launch_impl(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
