@@ -154,8 +154,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
             Segment sg;
             const uint32_t tx = static_cast<uint32_t>(kRowsW + x_pad) * kBKBytes;
             for (int si = 0; alive && segment_of(sched, worker, x_pad, si, &sg); ++si) {
-                int tm, tn;
-                tile_coord(sched, sg.tile, &tm, &tn);
+                const int tm = sg.tile;  // one column of tiles (tiles_n == 1): the tile's index is its row block of W
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const uint32_t s = it % kP, r = it / kP;
                     if (!mbar_wait(pk_empty(s), (r & 1u) ^ 1u, abort_flag)) { alive = false; break; }
@@ -216,8 +215,7 @@ gemm_s4_fewrows_kernel(const __grid_constant__ CUtensorMap tm_w,
         // kernel has completed.
         if (sched.sk_tiles > 0) asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int si = 0; alive && segment_of(sched, worker, x_pad, si, &sg); ++si, ++local_tile) {
-            int tm, tn;
-            tile_coord(sched, sg.tile, &tm, &tn);
+            const int tm = sg.tile;
             const uint32_t buf = local_tile & 1u, br = local_tile >> 1;
             if (!mbar_wait_warp(tm_full(buf), br & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
