@@ -28,15 +28,15 @@
 // Replaces, for these shapes, kernels/linear_v21.h:471-753 run on a 256 x 128 tile of padding.
 //
 // Tensor memory (512 columns): two accumulator buffers of two accumulators (one per issuing thread)
-// of 64 columns, then the stages of 64 columns
-// for W (lane = W row; 32-bit column c of a stage holds bytes 4c .. 4c+3 of the expanded row; UMMA j of
+// of 64 columns, then the stages of 64 columns for W (lane = W row; 32-bit column c of a stage holds bytes 4c .. 4c+3 of the expanded row; UMMA j of
 // a K step reads columns 8j .. 8j+7).  The expanded row is [even elements of packed chunk j | odd
 // elements of packed chunk j] for j = 0 .. 7 -- the order the X rows have in shared memory, so both
 // operands carry the same permutation of K.
 //
 // Work is handed out by the same schedule as in the main kernel (schedule.cuh) over tiles of Y
 // transposed: whole tiles round-robin, the last wave cut along K with the shares added into Y
-// (atomic adds; a clearing kernel runs in front, see gemm_tcgen05.cu).
+// (bulk reductions, or atomic adds where Y's row pitch forbids TMA; a clearing kernel runs in front,
+// see gemm_tcgen05.cu).
 #include "common.h"
 #include "ptx.cuh"
 #include "epilogue.cuh"
