@@ -82,10 +82,9 @@ I4L_HD long long sk_begin(const Schedule& s, int w)
 I4L_HD bool segment_of(const Schedule& s, int worker, int bn, int i, Segment* out)
 {
     const int items = s.whole + 2 * s.half_tiles;
-    const int mine = worker < items ? (items - worker + s.workers - 1) / s.workers : 0;
     Segment g;
-    if (i < mine) {
-        const int item = worker + i * s.workers;
+    const int item = worker + i * s.workers;  // (no division on this path: it runs before a kernel's first load)
+    if (item < items) {
         g.kb0 = 0;
         g.kb1 = s.kb_count;
         g.mode = kSegStore;
@@ -106,6 +105,7 @@ I4L_HD bool segment_of(const Schedule& s, int worker, int bn, int i, Segment* ou
     const long long u0 = sk_begin(s, worker), u1 = sk_begin(s, worker + 1);
     if (u1 <= u0) return false;
     const int ta = static_cast<int>(u0 / s.kb_count), tb = static_cast<int>((u1 - 1) / s.kb_count);
+    const int mine = worker < items ? (items - worker + s.workers - 1) / s.workers : 0;
     const int j = i - mine;
     int t;
     if (ta == tb) {
