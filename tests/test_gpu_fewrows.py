@@ -153,3 +153,32 @@ def test_fewrows_in_replayed_graphs_and_on_several_streams(cuda, fewrows_on):
             torch.cuda.synchronize()
             assert L.last_status() == 0
             assert all(bool((y == ref).all()) for y in outs), f"streams, {m} rows, tail {mode}"
+
+
+def test_fewrows_random_shapes(cuda, fewrows_on):
+    """Seeded random shapes with up to 128 rows through the few-rows kernel (forced on, so that it also
+    takes the shapes the dispatcher would leave to the decode kernels or the 128-row tiles): ragged M, N
+    and K tails, N % 4 != 0 (per-thread stores, atomic adds), all three tail forms, with bias."""
+    import torch
+    rng = np.random.default_rng(20241125)
+    shapes = []
+    for _ in range(40):
+        m = int(rng.choice([rng.integers(1, 17), rng.integers(17, 65), rng.integers(65, 129)]))
+        n = int(rng.choice([rng.integers(1, 130), rng.integers(130, 1500), rng.integers(1500, 6000), 4 * rng.integers(1000, 5000)]))
+        k = 32 * int(rng.choice([rng.integers(1, 9), rng.integers(9, 80)]))
+        shapes.append((m, n, k))
+    for i, (m, n, k) in enumerate(shapes):
+        x, w, xp, wp = make_case(m, n, k, seed=400 + i)
+        ref = _reference(x, w)
+        xd, wd = torch.from_numpy(xp).to(cuda), torch.from_numpy(wp).to(cuda)
+        bias_h = ((np.arange(n) * 17) % 1999 - 999).astype(np.int32)
+        bias = torch.from_numpy(bias_h).to(cuda)
+        for mode in (-1, 0, 2):
+            L.set_tail(mode)
+            yd = torch.full((m, n), -5, dtype=torch.int32, device=cuda)
+            L.linear(xd, wd, out=yd)
+            yb = L.linear(xd, wd, bias=bias)
+            torch.cuda.synchronize()
+            assert O.is_same(yd.cpu().numpy(), ref), (m, n, k, mode)
+            assert O.is_same(yb.cpu().numpy(), ref + bias_h[None, :]), (m, n, k, mode, "bias")
+    assert L.last_status() == 0
