@@ -267,7 +267,7 @@ int int4_linear_set_tail(int mode);
  * and the epilogue writes it back transposed -- and passes W through tensor memory instead of shared
  * memory, so that neither the tensor pipe nor the nibble expansion is spent on a 128-row X tile
  * that is mostly padding.  -1 (default): by shape -- 17 <= M <= 64 (from 17 to 32 only on large
- * weights), 65 <= M <= 128 when N >= 4096, and M <= 16 where the decode kernels cannot run or K >
+ * weights), 65 <= M <= 128 when N >= 4096 (from 113 rows on: and K >= 4096), and M <= 16 where the decode kernels cannot run or K >
  * 8192; 0: never; 1: whenever M <= 128.  Results are identical either way.  The reference runs
  * every M on its one 256 x 128 tile (kernels/linear_v21.cu:12).
  * Returns INT4L_OK or INT4L_ERR_INVALID_ARG.  Environment: INT4L_FEWROWS=0|1. */

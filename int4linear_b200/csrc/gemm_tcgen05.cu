@@ -605,9 +605,10 @@ int launch_tcgen05(DeviceCtx* ctx, const Problem& p, cudaStream_t stream)
     }
     // A few rows of X: operands swapped and W through tensor memory (gemm_fewrows.cu).  From 65 rows on
     // only with at least 32 tiles of W rows: below that the 128 x 64 / 128 x 128 tiles of this kernel
-    // put more CTAs to work (128 x 1024 x 1024: 7.5 us here, 8.1 there; 128 x 6144 x 4096: 15.5 / 13.9).
+    // put more CTAs to work (128 x 1024 x 1024: 7.5 us here, 8.1 there; 128 x 6144 x 4096: 15.5 / 13.9);
+    // and from 113 rows on only with K >= 4096 (128 x 8192 x 1024: 8.5 us here, 9.1 there).
     if (fewrows_supports(p) && (fewrows_mode() == 1 || (fewrows_mode() < 0 && forced_tile_n() == 0 && forced_pairs() < 0 &&
-                                                          (p.m <= 64 || p.n >= 4096))))
+                                                          (p.m <= 64 || (p.n >= 4096 && (p.m <= 112 || p.k >= 4096))))))
         return launch_fewrows(ctx, p, stream);
     // Tile choice by a small cost model fitted to measurements on B200: cost = (tile times the
     // busiest worker runs) x (time of one tile relative to a 256 x 256 pair tile).  A wider tile
